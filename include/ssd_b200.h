@@ -1,0 +1,252 @@
+/*
+ * ssd_b200.h -- C ABI of libssd_b200.so: the Mamba2 SSD forward hot path on NVIDIA B200
+ * (sm_100a): chunk cumsum of dt*A, per-chunk state, inter-chunk state passing, their
+ * fused form, and the two chunk GEMM steps (C.B^T and the chunk scan) that the
+ * end-to-end forward check needs.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer on the device that is current when the call is
+ *     made; every call only enqueues work on `stream` and returns without synchronising.
+ *   - Strides are in ELEMENTS, not bytes.  Shapes use: b batch, l seqlen, h nheads,
+ *     p headdim, g ngroups, n dstate, L chunk_size, c = ceil(l / L) nchunks.
+ *   - Optional tensors are NULL when absent.
+ *   - Return value: SSD_OK or an ssd_status_t error; ssd_last_error() gives a message for
+ *     the calling thread.  No call allocates device memory except where stated; scratch
+ *     memory is supplied by the caller (see ssd_fused_state_workspace_bytes).
+ *   - The library contains sm_100a code only.  On any other device the launch fails and
+ *     the call returns SSD_ERR_CUDA; there is no CPU path.
+ *
+ * Each entry point names the function of the reference project
+ * (RishiAstra/mamba-fused-minimal, paths relative to its root) whose device work it
+ * replaces.
+ */
+#ifndef SSD_B200_H_
+#define SSD_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SSD_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define SSD_API __attribute__((visibility("default")))
+#else
+#define SSD_API
+#endif
+
+typedef struct CUstream_st* ssd_stream_t; /* a cudaStream_t / CUstream handle */
+
+typedef enum {
+  SSD_F32 = 0,
+  SSD_BF16 = 1,
+  SSD_F16 = 2
+} ssd_dtype_t;
+
+typedef enum {
+  SSD_OK = 0,
+  SSD_ERR_BAD_ARGUMENT = 1, /* null pointer, non-positive size, inconsistent shapes        */
+  SSD_ERR_UNSUPPORTED = 2,  /* a combination this build has no kernel for                  */
+  SSD_ERR_CUDA = 3,         /* the CUDA runtime / driver reported an error on launch       */
+  SSD_ERR_WORKSPACE = 4,    /* workspace missing, misaligned or too small                  */
+  SSD_ERR_TIMEOUT = 5       /* a bounded device-side wait gave up (see ssd_check_status)   */
+} ssd_status_t;
+
+/* Message for the last non-OK status returned to the calling thread ("" if none). */
+SSD_API const char* ssd_last_error(void);
+/* SSD_B200_ABI_VERSION the library was built with. */
+SSD_API int ssd_abi_version(void);
+
+/* ------------------------------------------------------------------------------------
+ * 1. chunk cumsum.  Replaces _chunk_cumsum_fwd, kernels/ssd_chunk_state.py:176-199
+ *    (device code :33-79).
+ *    dt' = clamp(softplus?(dt + dt_bias), dt_min, dt_max), zero past seqlen;
+ *    dA_cumsum = inclusive cumsum over each chunk of dt' * A.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* dt;        /* (b, l, h), dt_dtype */
+  const void* A;         /* (h,), A_dtype */
+  const void* dt_bias;   /* (h,) or NULL, bias_dtype */
+  float* dt_out;         /* (b, h, c, L) contiguous fp32 */
+  float* dA_cumsum;      /* (b, h, c, L) contiguous fp32 */
+  int32_t dt_dtype, A_dtype, bias_dtype;
+  int32_t batch, seqlen, nheads, chunk_size;
+  int64_t dt_stride_b, dt_stride_l, dt_stride_h;
+  int64_t A_stride, bias_stride;
+  float dt_min, dt_max;
+  int32_t dt_softplus;   /* non-zero: softplus where dt + bias <= 20 */
+} ssd_chunk_cumsum_params_t;
+
+SSD_API int ssd_chunk_cumsum_fwd(const ssd_chunk_cumsum_params_t* prm, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Tensors shared by the state kernels.
+ *   x (b, l, h, p), B (b, l, g, n) of in_dtype; dt, dA_cumsum (b, h, c, L) fp32 with
+ *   element strides given as (b, h, c, L).  seq_idx (b, l) int32 or NULL.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  const void* B;
+  const float* dt;
+  const float* dA_cumsum;
+  const int32_t* seq_idx;
+  int32_t in_dtype;
+  int32_t batch, seqlen, nheads, headdim, ngroups, dstate, chunk_size;
+  int64_t x_stride[4];       /* b, l, h, p */
+  int64_t B_stride[4];       /* b, l, g, n */
+  int64_t dt_stride[4];      /* b, h, c, L */
+  int64_t dA_stride[4];      /* b, h, c, L */
+  int64_t seq_idx_stride[2]; /* b, l */
+} ssd_state_inputs_t;
+
+/* ------------------------------------------------------------------------------------
+ * 2. per-chunk state.  Replaces _chunk_state_fwd, kernels/ssd_chunk_state.py:202-232
+ *    (device code :97-173).
+ *    states[b,c,h,p,n] = sum_k x[k,p] * cast_in(B[k,n] * exp(min(dA_last - dA_k, 0)) * dt_k)
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  ssd_state_inputs_t in;
+  void* states;              /* (b, c, h, p, n) of states_dtype */
+  int32_t states_dtype;
+  int64_t states_stride[5];  /* b, c, h, p, n */
+} ssd_chunk_state_params_t;
+
+SSD_API int ssd_chunk_state_fwd(const ssd_chunk_state_params_t* prm, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * 3. state passing.  Replaces _state_passing_fwd, kernels/ssd_state_passing.py:87-115
+ *    (device code :27-84).
+ *    S = initial or 0; for each chunk: out[c] = S; S = exp(dA_chunk[c]) * S + states[c];
+ *    final = S.  S stays fp32.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* states;          /* (b, c, h, dim) of states_dtype */
+  const void* dA_chunk_cumsum; /* (b, h, c) of dA_dtype */
+  const void* initial_states;  /* (b, h, dim) of init_dtype, or NULL */
+  const int32_t* seq_idx;      /* (b, l) or NULL */
+  void* out;                   /* (b, c, h, dim) of out_dtype */
+  float* final_states;         /* (b, h, dim) fp32 */
+  int32_t states_dtype, dA_dtype, init_dtype, out_dtype;
+  int32_t batch, nchunks, nheads, dim;
+  int32_t seqlen, chunk_size;  /* used with seq_idx only */
+  int64_t states_stride[4];    /* b, c, h, dim */
+  int64_t dA_stride[3];        /* b, h, c */
+  int64_t init_stride[3];      /* b, h, dim */
+  int64_t out_stride[4];       /* b, c, h, dim */
+  int64_t final_stride[3];     /* b, h, dim */
+  int64_t seq_idx_stride[2];
+} ssd_state_passing_params_t;
+
+SSD_API int ssd_state_passing_fwd(const ssd_state_passing_params_t* prm, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * 4. fused chunk state + state passing, one launch.  Replaces both
+ *    _fused_chunk_state_state_passing_fwd_concurrent, kernels/fused_concurrent.py:255-331
+ *    (device code :17-252) and _fused_chunk_state_state_passing_fwd_globalbar,
+ *    kernels/fused_globalbar.py:201-266 (device code :16-198).
+ *
+ *    out[b,c,h,p,n]   the state entering chunk c (exclusive prefix), out_dtype
+ *    final[b,h,p,n]   the state after the last chunk, fp32
+ *    states           optional: the per-chunk states, written as in (2) when non-NULL
+ *
+ *    The fp32 per-chunk states never go to memory unless `states` is given.  The kernel
+ *    is persistent (one CTA per SM); each CTA walks a contiguous range of (b, h, chunk)
+ *    units and keeps the running state on chip.  Where a CTA's range starts in the middle
+ *    of a (b, h) sequence the carried state comes from the CTA that owns the preceding
+ *    range, through `workspace` and a flag; the wait on that flag is bounded, and a wait
+ *    that gives up sets a status word (see ssd_check_status).
+ *
+ *    `workspace`: ssd_fused_state_workspace_bytes() bytes, 256-byte aligned, owned by the
+ *    caller, used by one call at a time.  Its first 1 KiB must be zero on the first use
+ *    and is left zero-equivalent by every call (flags carry an epoch), so one buffer can
+ *    be reused by successive calls on the same stream without clearing.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  ssd_state_inputs_t in;
+  const void* initial_states; /* (b, h, p, n) of init_dtype, (p, n) contiguous, or NULL */
+  void* out;                  /* (b, c, h, p, n) of out_dtype, (p, n) contiguous */
+  float* final_states;        /* (b, h, p, n) fp32, (p, n) contiguous */
+  void* states;               /* optional (b, c, h, p, n) of states_dtype, (p, n) contiguous */
+  int32_t init_dtype, out_dtype, states_dtype;
+  int64_t init_stride[3];     /* b, h, p (n has stride 1) */
+  int64_t out_stride[4];      /* b, c, h, p */
+  int64_t final_stride[3];    /* b, h, p */
+  int64_t states_stride[4];   /* b, c, h, p */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t clamp_decay;        /* non-zero: exp(min(d, 0)) as the unfused kernel does
+                                 (ssd_chunk_state.py:153); zero: exp(d) as the reference's
+                                 fused kernels do (fused_concurrent.py:119).  Identical
+                                 whenever dt >= 0 and A <= 0. */
+  int32_t force_general;      /* non-zero: skip the tcgen05 kernel, use the plain kernels */
+} ssd_fused_state_params_t;
+
+SSD_API size_t ssd_fused_state_workspace_bytes(const ssd_fused_state_params_t* prm);
+SSD_API int ssd_fused_state_fwd(const ssd_fused_state_params_t* prm, ssd_stream_t stream);
+
+/* Reads back (synchronously, after synchronising `stream`) the status word that the last
+ * ssd_fused_state_fwd on this workspace left: SSD_OK, or SSD_ERR_TIMEOUT if a bounded
+ * device wait gave up (outputs are then incomplete).  Optional: a healthy run never sets
+ * it.  Has no counterpart in the reference, whose waits are unbounded
+ * (kernels/fused_concurrent.py:82-84,205-208). */
+SSD_API int ssd_check_status(void* workspace, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * 5. chunk bmm.  Replaces _bmm_chunk_fwd, kernels/ssd_bmm.py:89-134 (device code :31-87).
+ *    out[b,c,g,i,j] = sum_k a[b, c*L+i, g, k] * b[b, c*L+j, g, k]
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* a;             /* (b, l, g, k) of in_dtype */
+  const void* b;             /* (b, l, g, k) of in_dtype */
+  const int32_t* seq_idx;    /* (b, l) or NULL */
+  void* out;                 /* (b, c, g, L, L) of out_dtype */
+  int32_t in_dtype, out_dtype;
+  int32_t batch, seqlen, ngroups, k, chunk_size;
+  int32_t causal;            /* non-zero: tiles strictly above the diagonal are not written */
+  int64_t a_stride[4], b_stride[4]; /* b, l, g, k */
+  int64_t out_stride[5];     /* b, c, g, i, j */
+  int64_t seq_idx_stride[2];
+} ssd_bmm_chunk_params_t;
+
+SSD_API int ssd_bmm_chunk_fwd(const ssd_bmm_chunk_params_t* prm, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * 6. chunk scan.  Replaces _chunk_scan_fwd, kernels/ssd_chunk_scan.py:172-221
+ *    (device code :38-169).
+ *    out[m] = exp(dA_m) * C[m] . cast_C(prev_state) + sum_{k<=m} cast_x(cb[m,k] *
+ *             exp(min(dA_m - dA_k, 0)) * dt_k) * x[k] + D * x[m];  with z: out_x = that,
+ *             out = out_x * z * sigmoid(z).
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* cb;            /* (b, c, g, L, L) of cb_dtype */
+  const void* x;             /* (b, l, h, p) of in_dtype */
+  const float* dt;           /* (b, h, c, L) fp32 */
+  const float* dA_cumsum;    /* (b, h, c, L) fp32 */
+  const void* C;             /* (b, l, g, n) of in_dtype */
+  const void* states;        /* (b, c, h, p, n) of states_dtype: the PASSED states */
+  const void* D;             /* (h,) or (h, p) of D_dtype, or NULL */
+  const void* z;             /* (b, l, h, p) of in_dtype, or NULL */
+  const int32_t* seq_idx;    /* (b, l) or NULL */
+  void* out;                 /* (b, l, h, p) of in_dtype */
+  void* out_x;               /* (b, l, h, p) of in_dtype; required when z is given */
+  int32_t cb_dtype, in_dtype, states_dtype, D_dtype;
+  int32_t batch, seqlen, nheads, headdim, ngroups, dstate, chunk_size;
+  int32_t D_has_hdim;        /* non-zero: D is (h, p) */
+  int64_t cb_stride[5];      /* b, c, g, m, k */
+  int64_t x_stride[4], z_stride[4], out_stride[4]; /* b, l, h, p */
+  int64_t dt_stride[4], dA_stride[4];              /* b, h, c, L */
+  int64_t C_stride[4];       /* b, l, g, n */
+  int64_t states_stride[5];  /* b, c, h, p, n */
+  int64_t D_stride;          /* per head */
+  int64_t seq_idx_stride[2];
+} ssd_chunk_scan_params_t;
+
+SSD_API int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSD_B200_H_ */

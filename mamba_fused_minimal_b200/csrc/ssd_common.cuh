@@ -1,0 +1,74 @@
+// Shared device/host helpers for libssd_b200: dtype-erased loads and stores, error
+// reporting for the C ABI, small math helpers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "ssd_b200.h"
+
+namespace ssd {
+
+// ---- error reporting -----------------------------------------------------------------
+void set_error(const char* fmt, ...);            // defined in ssd_abi.cu
+const char* get_error();
+
+#define SSD_REQUIRE(cond, status, ...)                                                    \
+  do {                                                                                    \
+    if (!(cond)) {                                                                        \
+      ::ssd::set_error(__VA_ARGS__);                                                      \
+      return (status);                                                                    \
+    }                                                                                     \
+  } while (0)
+
+#define SSD_CUDA_OK(expr)                                                                 \
+  do {                                                                                    \
+    cudaError_t e__ = (expr);                                                             \
+    if (e__ != cudaSuccess) {                                                             \
+      ::ssd::set_error("%s failed: %s", #expr, cudaGetErrorString(e__));                  \
+      return SSD_ERR_CUDA;                                                                \
+    }                                                                                     \
+  } while (0)
+
+inline bool valid_dtype(int d) { return d == SSD_F32 || d == SSD_BF16 || d == SSD_F16; }
+inline int dtype_size(int d) { return d == SSD_F32 ? 4 : 2; }
+
+// ---- dtype-erased element access -----------------------------------------------------
+__device__ __forceinline__ float load_f(const void* base, int dtype, int64_t idx) {
+  switch (dtype) {
+    case SSD_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);
+    case SSD_F16: return __half2float(static_cast<const __half*>(base)[idx]);
+    default: return static_cast<const float*>(base)[idx];
+  }
+}
+
+__device__ __forceinline__ void store_f(void* base, int dtype, int64_t idx, float v) {
+  switch (dtype) {
+    case SSD_BF16: static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v); break;
+    case SSD_F16: static_cast<__half*>(base)[idx] = __float2half_rn(v); break;
+    default: static_cast<float*>(base)[idx] = v; break;
+  }
+}
+
+// Round a float to `dtype` and back: the reference's "cast to the input type before the
+// dot product" rounding points.
+__device__ __forceinline__ float round_to(float v, int dtype) {
+  switch (dtype) {
+    case SSD_BF16: return __bfloat162float(__float2bfloat16_rn(v));
+    case SSD_F16: return __half2float(__float2half_rn(v));
+    default: return v;
+  }
+}
+
+// log(exp(x) + 1) where x <= 20, x otherwise: the reference's softplus
+// (kernels/softplus.py:8-10 applied at kernels/ssd_chunk_state.py:70).
+__device__ __forceinline__ float softplus_ref(float x) {
+  return x <= 20.0f ? logf(expf(x) + 1.0f) : x;
+}
+
+}  // namespace ssd

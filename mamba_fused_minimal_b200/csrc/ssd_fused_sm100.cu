@@ -1,0 +1,679 @@
+// Fused per-chunk state + inter-chunk state passing for sm_100a.
+//
+// One persistent CTA per SM.  The (batch, head-group-of-HPC, chunk) work items, ordered
+// strip-major (a "strip" is one batch element and HPC adjacent heads of one B/C group)
+// and chunk-minor, are cut into one contiguous range per CTA, so a CTA walks whole strips
+// chunk after chunk and keeps the running fp32 state of each head in registers.  Only
+// where a range boundary falls inside a strip does a state cross CTAs, through a carry
+// slot in global memory guarded by an epoch-stamped flag.  A CTA whose range ends inside a
+// strip processes that (dependency-free) head segment FIRST and its own dependent tail
+// segment LAST, so in the common case the carry it needs was published long before it is
+// asked for; when strips are longer than a CTA's range the wait is real, but it only holds
+// up the epilogue warps: the loads and MMAs of up to NBUF chunks run ahead of it.
+//
+// Per chunk and head: states^T[n, p] = sum_k Bs[k, n] * x[k, p] with
+// Bs = cast_in(B * exp(min(dA_last - dA_k, 0)) * dt_k)   (the reference's rounding point,
+// kernels/ssd_chunk_state.py:153-159), a 128 x 64 x L contraction done by tcgen05.mma with
+// the accumulator in TMEM (lanes = dstate index n, columns = headdim index p).
+//
+// Warp roles (HPC = heads per CTA sharing one B tile):
+//   warps [0, 4*HPC)      epilogue: one warpgroup per head; tcgen05.ld the chunk state,
+//                         S <- exp(dA_last) * S + state in registers, store out / final
+//   warp  4*HPC           TMA producer (x, B tiles; dt / dA_cumsum rows)
+//   warp  4*HPC + 1       MMA issuer (one thread), TMEM allocation
+//   remaining warps       scale B by the per-position decay*dt in fp32, round to the input
+//                         type, write the MMA's A operand (generic -> async proxy fence)
+#include <cuda.h>
+
+#include <mutex>
+
+#include "sm100_ptx.cuh"
+#include "ssd_common.cuh"
+#include "ssd_launch.h"
+
+namespace ssd {
+namespace {
+
+using namespace ptx;
+
+constexpr int kP = 64;        // headdim
+constexpr int kN = 128;       // dstate
+constexpr int kKT = 64;       // sequence positions per pipeline stage
+constexpr int kMaxL = 256;    // largest chunk size
+
+enum WaitCode {
+  kWaitDdEmpty = 101, kWaitStageEmpty, kWaitDdFull, kWaitStageFull, kWaitBsEmpty, kWaitBsFull,
+  kWaitAccEmpty, kWaitAccFull, kWaitCarry, kWaitGroup
+};
+
+template <int HPC>
+struct Cfg {
+  static constexpr int NS = (HPC == 1) ? 5 : 4;       // TMA stages
+  static constexpr int NT = 4;                        // scaled-B tiles
+  static constexpr int ND = 2;                        // dt/dA row slots
+  static constexpr int NBUF = 4;                      // TMEM accumulators per head
+  static constexpr int EPI_WARPS = 4 * HPC;
+  static constexpr int SCALE_WARPS = (HPC == 1) ? 6 : 6;
+  static constexpr int WARPS = EPI_WARPS + 2 + SCALE_WARPS;
+  static constexpr int THREADS = WARPS * 32;
+  static constexpr int SCALE_THREADS = SCALE_WARPS * 32;
+  static constexpr int RAWB_BYTES = kKT * kN * 2;     // 16 KiB: two 64-column SW128 boxes
+  static constexpr int X_BYTES = kKT * kP * 2;        // 8 KiB: one SW128 box
+  static constexpr int STAGE_BYTES = RAWB_BYTES + HPC * X_BYTES;
+  static constexpr int TMEM_COLS = HPC * NBUF * kP;   // 256 or 512
+  // shared-memory map (byte offsets from a 1024-aligned base)
+  static constexpr int OFF_STAGES = 0;
+  static constexpr int OFF_BS = OFF_STAGES + NS * STAGE_BYTES;
+  static constexpr int OFF_DTDA = OFF_BS + NT * RAWB_BYTES;
+  static constexpr int DTDA_SLOT = HPC * 2 * kMaxL * 4;
+  static constexpr int OFF_SCALE = OFF_DTDA + ND * DTDA_SLOT;
+  static constexpr int SCALE_SLOT = HPC * kMaxL * 4;
+  static constexpr int OFF_BARS = OFF_SCALE + 2 * SCALE_SLOT;
+  static constexpr int NUM_BARS = 2 * NS + 2 * NT + 2 * ND + NBUF + HPC * NBUF + 1 + HPC;
+  static constexpr int OFF_CTL = OFF_BARS + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = OFF_CTL + 64 + 1024;   // + alignment slack
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+  static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns must be a power of two");
+};
+
+struct FusedArgs {
+  const float* dt;
+  const float* dA;
+  const void* init;
+  void* out;
+  float* final_states;
+  void* states;
+  int* status;            // workspace header: [0] status, [1] epoch, [2] done counter
+  uint32_t* flags;        // [cta][HPC]
+  float* carry;           // [cta][HPC][kP * kN]
+  int64_t dt_s[3], dA_s[3];                 // b, h, c strides (elements); L stride is 1
+  int64_t init_s[3], out_s[4], final_s[3], states_s[4];
+  int batch, seqlen, nheads, ngroups, chunk_size, nchunks;
+  int strips_per_batch;   // nheads / HPC
+  int init_dtype, out_dtype, states_dtype;
+  int clamp_decay;
+  int mode;               // 0: state passing fused; 1: per-chunk states only
+};
+
+struct Range {
+  long long lo, hi;
+  int s_first, m;
+  bool rot;
+};
+
+__device__ __forceinline__ Range make_range(long long total, int nchunks) {
+  Range r;
+  r.lo = total * (long long)blockIdx.x / gridDim.x;
+  r.hi = total * (long long)(blockIdx.x + 1) / gridDim.x;
+  r.s_first = (int)(r.lo / nchunks);
+  const int s_last = (int)((r.hi - 1) / nchunks);
+  r.m = s_last - r.s_first + 1;
+  r.rot = (r.m > 1) && (r.hi % nchunks != 0);
+  return r;
+}
+
+// j-th segment of this CTA in processing order: the trailing head segment (if the range
+// ends inside a strip) first, whole strips next, the leading (possibly dependent) one last.
+__device__ __forceinline__ void get_segment(const Range& r, int nchunks, int j, int& strip,
+                                            int& c0, int& c1) {
+  int k;
+  if (r.m == 1) k = 0;
+  else if (r.rot) k = (j == 0) ? r.m - 1 : ((j == r.m - 1) ? 0 : j);
+  else k = (j == r.m - 1) ? 0 : j + 1;
+  strip = r.s_first + k;
+  const long long base = (long long)strip * nchunks;
+  c0 = (int)((r.lo > base ? r.lo : base) - base);
+  const long long end = base + nchunks;
+  c1 = (int)((r.hi < end ? r.hi : end) - base);
+}
+
+template <typename T> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+  static constexpr uint32_t kFmt = 1;
+  __device__ static __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  }
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <> struct Pack<__half> {
+  static constexpr uint32_t kFmt = 0;
+  __device__ static __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+__device__ __forceinline__ uint32_t pack16(int dtype, float lo, float hi) {
+  return dtype == SSD_BF16 ? Pack<__nv_bfloat16>::pack(lo, hi) : Pack<__half>::pack(lo, hi);
+}
+
+// Store 32 values v[i] = element (p0 + i, n) of a (kP x kN) row-major matrix whose rows
+// start at `row0` (element pointer to (p0, 0)), row pitch `pitch` elements.  Thread `n`.
+// fp32: one coalesced 128-byte row segment per warp instruction.  16-bit: neighbouring
+// lanes swap one value so that each lane stores one packed pair (n, n+1) of one row.
+__device__ __forceinline__ void store_rows32(void* base, int dtype, int64_t elem_off, int64_t pitch,
+                                             int n, const float (&v)[32]) {
+  if (dtype == SSD_F32) {
+    float* o = static_cast<float*>(base) + elem_off + n;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[(int64_t)i * pitch] = v[i];
+  } else {
+    const bool odd = n & 1;
+    uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(base) + elem_off +
+                                              (odd ? pitch + n - 1 : n));
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      // even lane keeps row i and sends its row i+1 value; odd lane the other way round
+      const float send = odd ? v[i] : v[i + 1];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+      const uint32_t w = odd ? pack16(dtype, recv, v[i + 1]) : pack16(dtype, v[i], recv);
+      o[(int64_t)i * pitch / 2] = w;
+    }
+  }
+}
+
+template <typename T, int HPC>
+__global__ void __launch_bounds__(Cfg<HPC>::THREADS, 1)
+fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                   const __grid_constant__ CUtensorMap tmap_B, const FusedArgs a) {
+  using C = Cfg<HPC>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // barrier addresses
+  const uint32_t bars = sbase + C::OFF_BARS;
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_empty = [&](int s) { return bars + 8u * (C::NS + s); };
+  auto bar_bs_full = [&](int t) { return bars + 8u * (2 * C::NS + t); };
+  auto bar_bs_empty = [&](int t) { return bars + 8u * (2 * C::NS + C::NT + t); };
+  auto bar_dd_full = [&](int r) { return bars + 8u * (2 * C::NS + 2 * C::NT + r); };
+  auto bar_dd_empty = [&](int r) { return bars + 8u * (2 * C::NS + 2 * C::NT + C::ND + r); };
+  auto bar_acc_full = [&](int b) { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + b); };
+  auto bar_acc_empty = [&](int hd, int b) {
+    return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + hd * C::NBUF + b);
+  };
+  // group barriers (an mbarrier instead of bar.sync so that the wait is bounded like the rest)
+  auto bar_sc_sync = [&]() { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF); };
+  auto bar_epi_sync = [&](int hd) {
+    return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF + 1 + hd);
+  };
+  volatile int* ctl = reinterpret_cast<volatile int*>(smem + C::OFF_CTL);   // [0] abort, [1] tmem, [2] epoch
+  WaitCtx wc{ctl, a.status};
+
+  if (tid == 0) {
+    for (int s = 0; s < C::NS; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    for (int t = 0; t < C::NT; ++t) { mbar_init(bar_bs_full(t), C::SCALE_WARPS); mbar_init(bar_bs_empty(t), 1); }
+    for (int r = 0; r < C::ND; ++r) { mbar_init(bar_dd_full(r), 1); mbar_init(bar_dd_empty(r), 1); }
+    for (int b = 0; b < C::NBUF; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_acc_empty(hd, b), 4);
+    }
+    mbar_init(bar_sc_sync(), C::SCALE_THREADS);
+    for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_epi_sync(hd), 128);
+    ctl[0] = 0;
+    ctl[2] = reinterpret_cast<volatile int*>(a.status)[1];     // epoch of the previous launch
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == C::EPI_WARPS + 1) {
+    tmem_alloc(sbase + C::OFF_CTL + 4, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == C::EPI_WARPS && lane == 0) {
+    prefetch_tensormap(&tmap_x);
+    prefetch_tensormap(&tmap_B);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = static_cast<uint32_t>(ctl[1]);
+  const uint32_t epoch_target = static_cast<uint32_t>(ctl[2]) + 1u;
+
+  const int L = a.chunk_size;
+  const int nchunks = a.nchunks;
+  const long long total = (long long)a.batch * a.strips_per_batch * nchunks;
+  const Range rg = make_range(total, nchunks);
+  const int ratio = a.nheads / a.ngroups;
+
+  if (warp == C::EPI_WARPS) {
+    // ============================== TMA producer ======================================
+    if (lane == 0) {
+      uint32_t it = 0, item = 0;
+      bool ok = true;
+      for (int j = 0; j < rg.m && ok; ++j) {
+        int strip, c0, c1;
+        get_segment(rg, nchunks, j, strip, c0, c1);
+        const int b = strip / a.strips_per_batch;
+        const int h0 = (strip % a.strips_per_batch) * HPC;
+        const int g = h0 / ratio;
+        for (int c = c0; c < c1 && ok; ++c, ++item) {
+          const int r = item % C::ND;
+          ok = mbar_wait(bar_dd_empty(r), ((item / C::ND) & 1) ^ 1, wc, kWaitDdEmpty);
+          if (!ok) break;
+          mbar_expect_tx(bar_dd_full(r), HPC * 2 * L * 4);
+#pragma unroll
+          for (int hd = 0; hd < HPC; ++hd) {
+            const uint32_t dst = sbase + C::OFF_DTDA + r * C::DTDA_SLOT + hd * 2 * kMaxL * 4;
+            bulk_load(dst, a.dt + (int64_t)b * a.dt_s[0] + (int64_t)(h0 + hd) * a.dt_s[1] + (int64_t)c * a.dt_s[2],
+                      L * 4, bar_dd_full(r));
+            bulk_load(dst + kMaxL * 4, a.dA + (int64_t)b * a.dA_s[0] + (int64_t)(h0 + hd) * a.dA_s[1] + (int64_t)c * a.dA_s[2],
+                      L * 4, bar_dd_full(r));
+          }
+          const int limit = min(L, a.seqlen - c * L);
+          const int ksteps = (limit + kKT - 1) / kKT;
+          for (int ks = 0; ks < ksteps; ++ks, ++it) {
+            const int s = it % C::NS;
+            ok = mbar_wait(bar_empty(s), ((it / C::NS) & 1) ^ 1, wc, kWaitStageEmpty);
+            if (!ok) break;
+            mbar_expect_tx(bar_full(s), C::STAGE_BYTES);
+            const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
+            const int l0 = c * L + ks * kKT;
+            tma_load_4d(st, &tmap_B, bar_full(s), 0, g, l0, b);
+            tma_load_4d(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b);
+#pragma unroll
+            for (int hd = 0; hd < HPC; ++hd)
+              tma_load_4d(st + C::RAWB_BYTES + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b);
+          }
+        }
+      }
+    }
+  } else if (warp == C::EPI_WARPS + 1) {
+    // ============================== MMA issuer ========================================
+    if (lane == 0) {
+      constexpr uint32_t idesc = mma_idesc(Pack<T>::kFmt, true, true, kN, kP);
+      uint32_t it = 0, item = 0, tcount = 0;
+      bool ok = true;
+      for (int j = 0; j < rg.m && ok; ++j) {
+        int strip, c0, c1;
+        get_segment(rg, nchunks, j, strip, c0, c1);
+        for (int c = c0; c < c1 && ok; ++c, ++item) {
+          const int buf = item % C::NBUF;
+#pragma unroll
+          for (int hd = 0; hd < HPC; ++hd) {
+            if (ok) ok = mbar_wait(bar_acc_empty(hd, buf), ((item / C::NBUF) & 1) ^ 1, wc, kWaitAccEmpty);
+          }
+          if (!ok) break;
+          tc_fence_after();
+          const int limit = min(L, a.seqlen - c * L);
+          const int ksteps = (limit + kKT - 1) / kKT;
+          for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+            const int s = it % C::NS;
+            ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
+            if (!ok) break;
+            const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
+#pragma unroll
+            for (int hd = 0; hd < HPC; ++hd) {
+              const int t = tcount % C::NT;
+              ok = mbar_wait(bar_bs_full(t), (tcount / C::NT) & 1, wc, kWaitBsFull);
+              if (!ok) break;
+              tc_fence_after();
+              const uint32_t a_base = sbase + C::OFF_BS + t * C::RAWB_BYTES;
+              const uint32_t b_base = st + C::RAWB_BYTES + hd * C::X_BYTES;
+              const uint32_t d_tmem = tmem_base + (hd * C::NBUF + buf) * kP;
+#pragma unroll
+              for (int k16 = 0; k16 < kKT / 16; ++k16) {
+                const uint64_t ad = smem_desc_sw128(a_base + k16 * 2048, C::RAWB_BYTES / 2, 1024);
+                const uint64_t bd = smem_desc_sw128(b_base + k16 * 2048, C::X_BYTES, 1024);
+                mma_f16_ss(d_tmem, ad, bd, idesc, (ks | k16) != 0 ? 1u : 0u);
+              }
+              mma_commit(bar_bs_empty(t));
+              ++tcount;
+            }
+            if (ok) mma_commit(bar_empty(s));
+          }
+          if (ok) mma_commit(bar_acc_full(buf));
+        }
+      }
+    }
+  } else if (warp >= C::EPI_WARPS + 2) {
+    // ============================== B scaling =========================================
+    const int stid = tid - (C::EPI_WARPS + 2) * 32;
+    uint32_t it = 0, item = 0, tcount = 0;
+    bool ok = true;
+    for (int j = 0; j < rg.m && ok; ++j) {
+      int strip, c0, c1;
+      get_segment(rg, nchunks, j, strip, c0, c1);
+      for (int c = c0; c < c1 && ok; ++c, ++item) {
+        const int r = item % C::ND;
+        ok = mbar_wait(bar_dd_full(r), (item / C::ND) & 1, wc, kWaitDdFull);
+        if (!ok) break;
+        const float* dd = reinterpret_cast<const float*>(smem + C::OFF_DTDA + r * C::DTDA_SLOT);
+        float* sc = reinterpret_cast<float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
+        for (int i = stid; i < HPC * L; i += C::SCALE_THREADS) {
+          const int hd = i / L, k = i - hd * L;
+          const float* row = dd + hd * 2 * kMaxL;
+          float d = row[kMaxL + L - 1] - row[kMaxL + k];
+          if (a.clamp_decay) d = fminf(d, 0.0f);
+          sc[hd * kMaxL + k] = fast_exp(d) * row[k];
+        }
+        mbar_arrive(bar_sc_sync());
+        ok = mbar_wait(bar_sc_sync(), item & 1, wc, kWaitGroup);
+        if (!ok) break;
+        if (stid == 0) mbar_arrive(bar_dd_empty(r));
+        const int limit = min(L, a.seqlen - c * L);
+        const int ksteps = (limit + kKT - 1) / kKT;
+        for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+          const int s = it % C::NS;
+          ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
+          if (!ok) break;
+          const uint8_t* raw = smem + C::OFF_STAGES + s * C::STAGE_BYTES;
+#pragma unroll
+          for (int hd = 0; hd < HPC; ++hd) {
+            const int t = tcount % C::NT;
+            ok = mbar_wait(bar_bs_empty(t), ((tcount / C::NT) & 1) ^ 1, wc, kWaitBsEmpty);
+            if (!ok) break;
+            uint8_t* dst = smem + C::OFF_BS + t * C::RAWB_BYTES;
+            const float* sch = sc + hd * kMaxL + ks * kKT;
+            for (int i = stid; i < C::RAWB_BYTES / 16; i += C::SCALE_THREADS) {
+              const int off = i * 16;
+              const int row = (off & (C::RAWB_BYTES / 2 - 1)) >> 7;      // k within the stage
+              const float f = sch[row];
+              const uint4 v = *reinterpret_cast<const uint4*>(raw + off);
+              uint4 o;
+              float lo, hi;
+              Pack<T>::unpack(v.x, lo, hi); o.x = Pack<T>::pack(lo * f, hi * f);
+              Pack<T>::unpack(v.y, lo, hi); o.y = Pack<T>::pack(lo * f, hi * f);
+              Pack<T>::unpack(v.z, lo, hi); o.z = Pack<T>::pack(lo * f, hi * f);
+              Pack<T>::unpack(v.w, lo, hi); o.w = Pack<T>::pack(lo * f, hi * f);
+              *reinterpret_cast<uint4*>(dst + off) = o;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_bs_full(t));
+            ++tcount;
+          }
+        }
+      }
+    }
+  } else {
+    // ============================== epilogue ==========================================
+    const int hd = warp >> 2;
+    const int n = (warp & 3) * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float S[kP];
+    uint32_t item = 0, epi_syncs = 0;
+    bool ok = true;
+    for (int j = 0; j < rg.m && ok; ++j) {
+      int strip, c0, c1;
+      get_segment(rg, nchunks, j, strip, c0, c1);
+      const int b = strip / a.strips_per_batch;
+      const int h = (strip % a.strips_per_batch) * HPC + hd;
+      if (a.mode == 0) {
+        if (c0 == 0) {
+          if (a.init != nullptr) {
+            const int64_t ib = (int64_t)b * a.init_s[0] + (int64_t)h * a.init_s[1] + n;
+#pragma unroll
+            for (int p = 0; p < kP; ++p) S[p] = load_f(a.init, a.init_dtype, ib + (int64_t)p * a.init_s[2]);
+          } else {
+#pragma unroll
+            for (int p = 0; p < kP; ++p) S[p] = 0.0f;
+          }
+        } else {
+          const int src = (int)blockIdx.x - 1;
+          ok = flag_wait(a.flags + (size_t)src * HPC + hd, epoch_target, wc, kWaitCarry);
+          if (!ok) break;
+          const float* cin = a.carry + ((size_t)src * HPC + hd) * (kP * kN) + n;
+#pragma unroll
+          for (int p = 0; p < kP; ++p) S[p] = __ldcg(cin + p * kN);
+        }
+      }
+      for (int c = c0; c < c1 && ok; ++c, ++item) {
+        const int buf = item % C::NBUF;
+        float decay = 0.0f;
+        if (a.mode == 0)
+          decay = fast_exp(__ldg(a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2] + (L - 1)));
+        ok = mbar_wait(bar_acc_full(buf), (item / C::NBUF) & 1, wc, kWaitAccFull);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + lane_sel + (hd * C::NBUF + buf) * kP;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t raw[32];
+          tmem_ld_32x32(taddr + half * 32, raw);
+          tmem_ld_wait();
+          if (half == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty(hd, buf));
+          }
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+          if (a.states != nullptr) {
+            const int64_t so = (int64_t)b * a.states_s[0] + (int64_t)c * a.states_s[1] + (int64_t)h * a.states_s[2] +
+                               (int64_t)(half * 32) * a.states_s[3];
+            store_rows32(a.states, a.states_dtype, so, a.states_s[3], n, v);
+          }
+          if (a.mode == 0) {
+            float cur[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) cur[i] = S[half * 32 + i];
+            const int64_t oo = (int64_t)b * a.out_s[0] + (int64_t)c * a.out_s[1] + (int64_t)h * a.out_s[2] +
+                               (int64_t)(half * 32) * a.out_s[3];
+            store_rows32(a.out, a.out_dtype, oo, a.out_s[3], n, cur);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) S[half * 32 + i] = fmaf(decay, cur[i], v[i]);
+          }
+        }
+      }
+      if (!ok || a.mode != 0) continue;
+      if (c1 == nchunks) {
+        float* fo = a.final_states + (int64_t)b * a.final_s[0] + (int64_t)h * a.final_s[1] + n;
+#pragma unroll
+        for (int p = 0; p < kP; ++p) fo[(int64_t)p * a.final_s[2]] = S[p];
+      } else {
+        float* co = a.carry + ((size_t)blockIdx.x * HPC + hd) * (kP * kN) + n;
+#pragma unroll
+        for (int p = 0; p < kP; ++p) __stcg(co + p * kN, S[p]);
+        __threadfence();
+        mbar_arrive(bar_epi_sync(hd));
+        ok = mbar_wait(bar_epi_sync(hd), epi_syncs & 1, wc, kWaitGroup);
+        ++epi_syncs;
+        if (!ok) break;
+        if ((tid & 127) == 0) st_release_gpu(a.flags + (size_t)blockIdx.x * HPC + hd, epoch_target);
+      }
+    }
+  }
+
+  // ================================ teardown ==========================================
+  if (ctl[0] != 0) {
+    // a wait gave up: give in-flight bulk copies time to land before the CTA retires
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == C::EPI_WARPS + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+  if (tid == 0) {
+    __threadfence();
+    const int prev = atomicAdd(a.status + 2, 1);
+    if (prev == (int)gridDim.x - 1) {
+      a.status[2] = 0;
+      __threadfence();
+      reinterpret_cast<volatile int*>(a.status)[1] = (int)epoch_target;
+    }
+  }
+}
+
+// Status / epoch / done words for launches in the states-only mode, which has no workspace.
+__device__ int g_states_only_header[64];
+
+// ---- host side ------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 4-D map over a (b, l, heads, inner) tensor whose innermost dimension is contiguous;
+// box = 64 inner elements x 1 head x kKT positions x 1 batch, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int dtype, int inner, int heads, int seqlen, int batch,
+             const int64_t* stride /* b, l, h, inner */) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)heads, (cuuint64_t)seqlen, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)stride[2] * 2, (cuuint64_t)stride[1] * 2, (cuuint64_t)stride[0] * 2};
+  const cuuint32_t box[4] = {64, 1, (cuuint32_t)kKT, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int num_sms() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (sms[dev] == 0) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    sms[dev] = v > 0 ? v : 1;
+  }
+  return sms[dev];
+}
+
+template <typename T, int HPC>
+int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream) {
+  using C = Cfg<HPC>;
+  const ssd_state_inputs_t& in = p.in;
+  CUtensorMap mx, mB;
+  int rc = make_map(&mx, in.x, in.in_dtype, kP, in.nheads, in.seqlen, in.batch, in.x_stride);
+  if (rc != SSD_OK) return rc;
+  rc = make_map(&mB, in.B, in.in_dtype, kN, in.ngroups, in.seqlen, in.batch, in.B_stride);
+  if (rc != SSD_OK) return rc;
+
+  FusedArgs a{};
+  a.dt = in.dt;
+  a.dA = in.dA_cumsum;
+  a.init = p.initial_states;
+  a.out = p.out;
+  a.final_states = p.final_states;
+  a.states = p.states;
+  if (p.workspace != nullptr) {
+    uint8_t* ws = static_cast<uint8_t*>(p.workspace);
+    a.status = reinterpret_cast<int*>(ws);
+    a.flags = reinterpret_cast<uint32_t*>(ws + FusedWorkspaceLayout::kHeaderBytes);
+    a.carry = reinterpret_cast<float*>(ws + FusedWorkspaceLayout::kCarryOffset);
+  } else {
+    SSD_REQUIRE(mode == 1, SSD_ERR_WORKSPACE, "workspace is NULL");
+    int* hdr = nullptr;
+    SSD_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&hdr), g_states_only_header));
+    a.status = hdr;
+  }
+  for (int i = 0; i < 3; ++i) {
+    a.dt_s[i] = in.dt_stride[i];
+    a.dA_s[i] = in.dA_stride[i];
+    a.init_s[i] = p.init_stride[i];
+    a.final_s[i] = p.final_stride[i];
+  }
+  for (int i = 0; i < 4; ++i) {
+    a.out_s[i] = p.out_stride[i];
+    a.states_s[i] = p.states_stride[i];
+  }
+  a.batch = in.batch;
+  a.seqlen = in.seqlen;
+  a.nheads = in.nheads;
+  a.ngroups = in.ngroups;
+  a.chunk_size = in.chunk_size;
+  a.nchunks = (in.seqlen + in.chunk_size - 1) / in.chunk_size;
+  a.strips_per_batch = in.nheads / HPC;
+  a.init_dtype = p.init_dtype;
+  a.out_dtype = p.out_dtype;
+  a.states_dtype = p.states_dtype;
+  a.clamp_decay = p.clamp_decay;
+  a.mode = mode;
+
+  const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
+  const int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
+  auto kern = fused_state_kernel<T, HPC>;
+  SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(mx, mB, a);
+  SSD_CUDA_OK(cudaGetLastError());
+  return SSD_OK;
+}
+
+}  // namespace
+
+int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why) {
+  const ssd_state_inputs_t& in = p.in;
+  auto no = [&](const char* m) { if (why) *why = m; return 0; };
+  if (in.in_dtype != SSD_BF16 && in.in_dtype != SSD_F16) return no("inputs are not bf16/fp16");
+  if (in.headdim != kP || in.dstate != kN) return no("headdim != 64 or dstate != 128");
+  if (in.chunk_size % kKT != 0 || in.chunk_size > kMaxL) return no("chunk_size not a multiple of 64 up to 256");
+  if (in.seq_idx != nullptr) return no("seq_idx given");
+  if (in.x_stride[3] != 1 || in.B_stride[3] != 1) return no("x or B innermost stride != 1");
+  if (!aligned16(in.x) || !aligned16(in.B)) return no("x or B not 16-byte aligned");
+  for (int i = 0; i < 3; ++i)
+    if (in.x_stride[i] % 8 != 0 || in.B_stride[i] % 8 != 0) return no("x or B stride not a multiple of 16 bytes");
+  if (in.dt_stride[3] != 1 || in.dA_stride[3] != 1) return no("dt or dA_cumsum innermost stride != 1");
+  if (!aligned16(in.dt) || !aligned16(in.dA_cumsum)) return no("dt or dA_cumsum not 16-byte aligned");
+  for (int i = 0; i < 3; ++i)
+    if (in.dt_stride[i] % 4 != 0 || in.dA_stride[i] % 4 != 0) return no("dt or dA_cumsum stride not a multiple of 16 bytes");
+  auto rows_ok = [&](const void* ptr, int dtype, const int64_t* s, int ns) {
+    if (ptr == nullptr) return true;
+    if (s[ns - 1] != kN) return false;                      // (p, n) contiguous
+    if ((reinterpret_cast<uintptr_t>(ptr) & 3) != 0) return false;
+    if (dtype != SSD_F32)
+      for (int i = 0; i < ns; ++i)
+        if (s[i] % 2 != 0) return false;                    // packed pair stores
+    return true;
+  };
+  if (!rows_ok(p.out, p.out_dtype, p.out_stride, 4)) return no("out layout");
+  if (!rows_ok(p.states, p.states_dtype, p.states_stride, 4)) return no("states layout");
+  if (p.final_states != nullptr && p.final_stride[2] != kN) return no("final_states layout");
+  if (p.initial_states != nullptr && p.init_stride[2] != kN) return no("initial_states layout");
+  const int ratio = in.nheads / in.ngroups;
+  if (why) *why = "";
+  return (ratio % 2 == 0) ? 2 : 1;
+}
+
+size_t fused_fast_workspace_bytes(const ssd_fused_state_params_t&) {
+  return FusedWorkspaceLayout::kCarryOffset +
+         (size_t)FusedWorkspaceLayout::kMaxCtas * 2 * kP * kN * sizeof(float);
+}
+
+int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream) {
+  const int variant = fused_fast_variant(p, nullptr);
+  SSD_REQUIRE(variant != 0, SSD_ERR_UNSUPPORTED, "fused tcgen05 kernel cannot take this problem");
+  const bool bf16 = p.in.in_dtype == SSD_BF16;
+  if (variant == 2)
+    return bf16 ? launch_variant<__nv_bfloat16, 2>(p, mode, stream) : launch_variant<__half, 2>(p, mode, stream);
+  return bf16 ? launch_variant<__nv_bfloat16, 1>(p, mode, stream) : launch_variant<__half, 1>(p, mode, stream);
+}
+
+}  // namespace ssd

@@ -1,0 +1,32 @@
+// Internal launch interface between the C ABI (ssd_abi.cu) and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "ssd_b200.h"
+
+namespace ssd {
+
+// ---- general kernels (ssd_general.cu) -------------------------------------------------
+int launch_chunk_cumsum(const ssd_chunk_cumsum_params_t& p, cudaStream_t stream);
+int launch_state_passing(const ssd_state_passing_params_t& p, cudaStream_t stream);
+int launch_chunk_state_general(const ssd_chunk_state_params_t& p, int clamp_decay, cudaStream_t stream);
+int launch_bmm_chunk_general(const ssd_bmm_chunk_params_t& p, cudaStream_t stream);
+int launch_chunk_scan_general(const ssd_chunk_scan_params_t& p, cudaStream_t stream);
+
+// ---- tcgen05 fused state kernel (ssd_fused_sm100.cu) ----------------------------------
+// Layout of the caller-supplied workspace used by the fused kernel.
+struct FusedWorkspaceLayout {
+  static constexpr size_t kHeaderBytes = 256;      // status, epoch, done counter
+  static constexpr size_t kFlagsBytes = 4096 - 256;  // one word per (CTA, head slot)
+  static constexpr size_t kCarryOffset = 4096;
+  static constexpr int kMaxCtas = 160;             // flags: kMaxCtas * 2 words
+};
+
+// Which heads-per-CTA variant (0 = the fast kernel cannot take this problem).
+int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why);
+size_t fused_fast_workspace_bytes(const ssd_fused_state_params_t& p);
+// mode 0: chunk state + state passing; mode 1: per-chunk states only (p.states required).
+int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream);
+
+}  // namespace ssd

@@ -1,0 +1,417 @@
+// PyTorch front end of libssd_b200: takes torch tensors, checks devices and dtypes,
+// allocates outputs the way the reference's wrappers do (torch.empty on the input's
+// device), looks up the current CUDA stream and calls the C ABI (include/ssd_b200.h).
+// Shape assertions live in the Python shims so that they raise AssertionError like the
+// reference; this layer raises RuntimeError for anything the C ABI rejects.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <limits>
+#include <map>
+#include <mutex>
+#include <optional>
+
+#include "ssd_b200.h"
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = std::optional<Tensor>;
+
+int dtype_code(const Tensor& t, const char* name) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return SSD_F32;
+    case at::kBFloat16: return SSD_BF16;
+    case at::kHalf: return SSD_F16;
+    default: TORCH_CHECK(false, name, ": dtype ", t.scalar_type(), " is not fp32 / bf16 / fp16");
+  }
+}
+int dtype_code(at::ScalarType st) {
+  switch (st) {
+    case at::kFloat: return SSD_F32;
+    case at::kBFloat16: return SSD_BF16;
+    case at::kHalf: return SSD_F16;
+    default: TORCH_CHECK(false, "dtype ", st, " is not fp32 / bf16 / fp16");
+  }
+}
+
+void check_cuda(const Tensor& t, const Tensor& like, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (libssd_b200 has no CPU path)");
+  TORCH_CHECK(t.device() == like.device(), name, " is on ", t.device(), ", expected ", like.device());
+}
+
+ssd_stream_t current_stream(const Tensor& t) {
+  return reinterpret_cast<ssd_stream_t>(c10::cuda::getCurrentCUDAStream(t.device().index()).stream());
+}
+
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == SSD_OK, what, " failed (status ", rc, "): ", ssd_last_error());
+}
+
+template <int N>
+void copy_strides(int64_t (&dst)[N], const Tensor& t, std::initializer_list<int> dims) {
+  int i = 0;
+  for (int d : dims) dst[i++] = t.stride(d);
+}
+
+Tensor as_int32(const Tensor& seq_idx) {
+  return seq_idx.scalar_type() == at::kInt ? seq_idx : seq_idx.to(at::kInt);
+}
+
+void fill_state_inputs(ssd_state_inputs_t& in, const Tensor& B, const Tensor& x, const Tensor& dt,
+                       const Tensor& dA, const OptTensor& seq_idx, Tensor& seq_idx_hold) {
+  check_cuda(B, x, "B");
+  check_cuda(dt, x, "dt");
+  check_cuda(dA, x, "dA_cumsum");
+  TORCH_CHECK(x.dim() == 4 && B.dim() == 4 && dt.dim() == 4 && dA.dim() == 4, "x, B, dt, dA_cumsum must be 4-D");
+  TORCH_CHECK(B.scalar_type() == x.scalar_type(), "B and x must have the same dtype");
+  TORCH_CHECK(dt.scalar_type() == at::kFloat && dA.scalar_type() == at::kFloat, "dt and dA_cumsum must be fp32");
+  in.x = x.data_ptr();
+  in.B = B.data_ptr();
+  in.dt = dt.data_ptr<float>();
+  in.dA_cumsum = dA.data_ptr<float>();
+  in.in_dtype = dtype_code(x, "x");
+  in.batch = x.size(0);
+  in.seqlen = x.size(1);
+  in.nheads = x.size(2);
+  in.headdim = x.size(3);
+  in.ngroups = B.size(2);
+  in.dstate = B.size(3);
+  in.chunk_size = dt.size(3);
+  copy_strides(in.x_stride, x, {0, 1, 2, 3});
+  copy_strides(in.B_stride, B, {0, 1, 2, 3});
+  copy_strides(in.dt_stride, dt, {0, 1, 2, 3});
+  copy_strides(in.dA_stride, dA, {0, 1, 2, 3});
+  in.seq_idx = nullptr;
+  if (seq_idx.has_value()) {
+    check_cuda(*seq_idx, x, "seq_idx");
+    seq_idx_hold = as_int32(*seq_idx);
+    in.seq_idx = seq_idx_hold.data_ptr<int32_t>();
+    in.seq_idx_stride[0] = seq_idx_hold.stride(0);
+    in.seq_idx_stride[1] = seq_idx_hold.stride(1);
+  }
+}
+
+// One zero-initialised workspace per device, grown on demand.  The fused kernel leaves its
+// header consistent after every call, so the buffer is reused without clearing; work on
+// one device is assumed to be issued from one stream at a time, as the reference does.
+struct Workspace {
+  Tensor buf;
+};
+std::mutex g_ws_mutex;
+std::map<int, Workspace> g_ws;
+
+Tensor get_workspace(const Tensor& like, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  Workspace& w = g_ws[like.device().index()];
+  if (!w.buf.defined() || (size_t)w.buf.numel() < bytes) {
+    w.buf = torch::zeros({(int64_t)bytes}, torch::dtype(torch::kUInt8).device(like.device()));
+  }
+  return w.buf;
+}
+
+// ---------------------------------------------------------------------------------------
+std::tuple<Tensor, Tensor> chunk_cumsum_fwd(const Tensor& dt, const Tensor& A, int64_t chunk_size,
+                                            const OptTensor& dt_bias, bool dt_softplus, double dt_min,
+                                            double dt_max) {
+  TORCH_CHECK(dt.is_cuda(), "dt must be a CUDA tensor (libssd_b200 has no CPU path)");
+  check_cuda(A, dt, "A");
+  TORCH_CHECK(dt.dim() == 3 && A.dim() == 1, "dt must be (batch, seqlen, nheads) and A (nheads,)");
+  c10::cuda::CUDAGuard guard(dt.device());
+  const int64_t batch = dt.size(0), seqlen = dt.size(1), nheads = dt.size(2);
+  const int64_t nchunks = (seqlen + chunk_size - 1) / chunk_size;
+  auto opts = torch::dtype(torch::kFloat).device(dt.device());
+  Tensor dt_out = torch::empty({batch, nheads, nchunks, chunk_size}, opts);
+  Tensor dA_cumsum = torch::empty({batch, nheads, nchunks, chunk_size}, opts);
+  ssd_chunk_cumsum_params_t p{};
+  p.dt = dt.data_ptr();
+  p.A = A.data_ptr();
+  p.dt_dtype = dtype_code(dt, "dt");
+  p.A_dtype = dtype_code(A, "A");
+  if (dt_bias.has_value()) {
+    check_cuda(*dt_bias, dt, "dt_bias");
+    p.dt_bias = dt_bias->data_ptr();
+    p.bias_dtype = dtype_code(*dt_bias, "dt_bias");
+    p.bias_stride = dt_bias->stride(0);
+  }
+  p.dt_out = dt_out.data_ptr<float>();
+  p.dA_cumsum = dA_cumsum.data_ptr<float>();
+  p.batch = batch;
+  p.seqlen = seqlen;
+  p.nheads = nheads;
+  p.chunk_size = chunk_size;
+  p.dt_stride_b = dt.stride(0);
+  p.dt_stride_l = dt.stride(1);
+  p.dt_stride_h = dt.stride(2);
+  p.A_stride = A.stride(0);
+  p.dt_min = static_cast<float>(dt_min);
+  p.dt_max = static_cast<float>(dt_max);
+  p.dt_softplus = dt_softplus ? 1 : 0;
+  check_rc(ssd_chunk_cumsum_fwd(&p, current_stream(dt)), "ssd_chunk_cumsum_fwd");
+  return {dA_cumsum, dt_out};
+}
+
+Tensor chunk_state_fwd(const Tensor& B, const Tensor& x, const Tensor& dt, const Tensor& dA_cumsum,
+                       const OptTensor& seq_idx, const OptTensor& states_in, bool states_in_fp32) {
+  TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor (libssd_b200 has no CPU path)");
+  c10::cuda::CUDAGuard guard(x.device());
+  ssd_chunk_state_params_t p{};
+  Tensor hold;
+  fill_state_inputs(p.in, B, x, dt, dA_cumsum, seq_idx, hold);
+  const int64_t nchunks = dt.size(2);
+  Tensor states;
+  if (states_in.has_value()) {
+    states = *states_in;
+    check_cuda(states, x, "states");
+  } else {
+    states = torch::empty({x.size(0), nchunks, x.size(2), x.size(3), B.size(3)},
+                          torch::dtype(states_in_fp32 ? at::kFloat : B.scalar_type()).device(x.device()));
+  }
+  p.states = states.data_ptr();
+  p.states_dtype = dtype_code(states, "states");
+  copy_strides(p.states_stride, states, {0, 1, 2, 3, 4});
+  check_rc(ssd_chunk_state_fwd(&p, current_stream(x)), "ssd_chunk_state_fwd");
+  return states;
+}
+
+std::tuple<Tensor, Tensor> state_passing_fwd(const Tensor& states, const Tensor& dA_chunk_cumsum,
+                                             const OptTensor& initial_states, const OptTensor& seq_idx,
+                                             int64_t chunk_size, std::optional<at::ScalarType> out_dtype) {
+  TORCH_CHECK(states.is_cuda(), "states must be a CUDA tensor (libssd_b200 has no CPU path)");
+  check_cuda(dA_chunk_cumsum, states, "dA_chunk_cumsum");
+  TORCH_CHECK(states.dim() == 4 && dA_chunk_cumsum.dim() == 3, "states must be 4-D, dA_chunk_cumsum 3-D");
+  c10::cuda::CUDAGuard guard(states.device());
+  const int64_t batch = states.size(0), nchunks = states.size(1), nheads = states.size(2), dim = states.size(3);
+  const at::ScalarType odt = out_dtype.value_or(states.scalar_type());
+  Tensor out = torch::empty({batch, nchunks, nheads, dim}, torch::dtype(odt).device(states.device()));
+  Tensor fin = torch::empty({batch, nheads, dim}, torch::dtype(at::kFloat).device(states.device()));
+  ssd_state_passing_params_t p{};
+  p.states = states.data_ptr();
+  p.states_dtype = dtype_code(states, "states");
+  p.dA_chunk_cumsum = dA_chunk_cumsum.data_ptr();
+  p.dA_dtype = dtype_code(dA_chunk_cumsum, "dA_chunk_cumsum");
+  Tensor hold;
+  if (initial_states.has_value()) {
+    check_cuda(*initial_states, states, "initial_states");
+    p.initial_states = initial_states->data_ptr();
+    p.init_dtype = dtype_code(*initial_states, "initial_states");
+    copy_strides(p.init_stride, *initial_states, {0, 1, 2});
+  }
+  if (seq_idx.has_value()) {
+    check_cuda(*seq_idx, states, "seq_idx");
+    hold = as_int32(*seq_idx);
+    p.seq_idx = hold.data_ptr<int32_t>();
+    p.seq_idx_stride[0] = hold.stride(0);
+    p.seq_idx_stride[1] = hold.stride(1);
+    p.seqlen = hold.size(1);
+    p.chunk_size = chunk_size;
+  }
+  p.out = out.data_ptr();
+  p.out_dtype = dtype_code(odt);
+  p.final_states = fin.data_ptr<float>();
+  p.batch = batch;
+  p.nchunks = nchunks;
+  p.nheads = nheads;
+  p.dim = dim;
+  copy_strides(p.states_stride, states, {0, 1, 2, 3});
+  copy_strides(p.dA_stride, dA_chunk_cumsum, {0, 1, 2});
+  copy_strides(p.out_stride, out, {0, 1, 2, 3});
+  copy_strides(p.final_stride, fin, {0, 1, 2});
+  check_rc(ssd_state_passing_fwd(&p, current_stream(states)), "ssd_state_passing_fwd");
+  return {out, fin};
+}
+
+std::tuple<Tensor, Tensor> fused_state_fwd(const Tensor& B, const Tensor& x, const Tensor& dt,
+                                           const Tensor& dA_cumsum, std::optional<at::ScalarType> out_dtype,
+                                           const OptTensor& initial_states, const OptTensor& seq_idx,
+                                           const OptTensor& states_in, bool states_in_fp32, bool clamp_decay,
+                                           bool force_general) {
+  TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor (libssd_b200 has no CPU path)");
+  c10::cuda::CUDAGuard guard(x.device());
+  ssd_fused_state_params_t p{};
+  Tensor hold;
+  fill_state_inputs(p.in, B, x, dt, dA_cumsum, seq_idx, hold);
+  const int64_t batch = x.size(0), nheads = x.size(2), headdim = x.size(3), dstate = B.size(3);
+  const int64_t nchunks = dt.size(2);
+  // The reference's fused wrappers allocate a full per-chunk states tensor when none is
+  // passed and take out_dtype's default from it (kernels/fused_concurrent.py:269-282).
+  // Here that intermediate is never materialised unless the caller asks for it.
+  const at::ScalarType states_dt = states_in.has_value() ? states_in->scalar_type()
+                                                         : (states_in_fp32 ? at::kFloat : B.scalar_type());
+  const at::ScalarType odt = out_dtype.value_or(states_dt);
+  Tensor out = torch::empty({batch, nchunks, nheads, headdim, dstate}, torch::dtype(odt).device(x.device()));
+  Tensor fin = torch::empty({batch, nheads, headdim, dstate}, torch::dtype(at::kFloat).device(x.device()));
+  if (initial_states.has_value()) {
+    check_cuda(*initial_states, x, "initial_states");
+    TORCH_CHECK(initial_states->stride(3) == 1, "initial_states must be contiguous in its last dimension");
+    p.initial_states = initial_states->data_ptr();
+    p.init_dtype = dtype_code(*initial_states, "initial_states");
+    copy_strides(p.init_stride, *initial_states, {0, 1, 2});
+  }
+  if (states_in.has_value()) {
+    check_cuda(*states_in, x, "states");
+    TORCH_CHECK(states_in->stride(4) == 1, "states must be contiguous in its last dimension");
+    p.states = states_in->data_ptr();
+    p.states_dtype = dtype_code(*states_in, "states");
+    copy_strides(p.states_stride, *states_in, {0, 1, 2, 3});
+  }
+  p.out = out.data_ptr();
+  p.out_dtype = dtype_code(odt);
+  copy_strides(p.out_stride, out, {0, 1, 2, 3});
+  p.final_states = fin.data_ptr<float>();
+  copy_strides(p.final_stride, fin, {0, 1, 2});
+  p.clamp_decay = clamp_decay ? 1 : 0;
+  p.force_general = force_general ? 1 : 0;
+  const size_t need = ssd_fused_state_workspace_bytes(&p);
+  Tensor ws = get_workspace(x, need);
+  p.workspace = ws.data_ptr();
+  p.workspace_bytes = ws.numel();
+  check_rc(ssd_fused_state_fwd(&p, current_stream(x)), "ssd_fused_state_fwd");
+  return {out, fin};
+}
+
+// Synchronises and reports whether the last fused call on this device hit a wait limit.
+void check_status(const Tensor& like) {
+  c10::cuda::CUDAGuard guard(like.device());
+  Tensor ws;
+  {
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    auto it = g_ws.find(like.device().index());
+    if (it == g_ws.end() || !it->second.buf.defined()) return;
+    ws = it->second.buf;
+  }
+  const int rc = ssd_check_status(ws.data_ptr(), current_stream(like));
+  if (rc == SSD_ERR_TIMEOUT) ws.zero_();
+  check_rc(rc, "ssd_check_status");
+}
+
+Tensor bmm_chunk_fwd(const Tensor& a, const Tensor& b, int64_t chunk_size, const OptTensor& seq_idx, bool causal,
+                     std::optional<at::ScalarType> output_dtype) {
+  TORCH_CHECK(a.is_cuda(), "a must be a CUDA tensor (libssd_b200 has no CPU path)");
+  check_cuda(b, a, "b");
+  TORCH_CHECK(a.dim() == 3 || a.dim() == 4, "a must be (batch, seqlen, k) or (batch, seqlen, ngroups, k)");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a and b must have the same dtype");
+  c10::cuda::CUDAGuard guard(a.device());
+  const bool has_groups = a.dim() == 4;
+  const Tensor a4 = has_groups ? a : a.unsqueeze(2);
+  const Tensor b4 = has_groups ? b : b.unsqueeze(2);
+  const int64_t batch = a4.size(0), seqlen = a4.size(1), ngroups = a4.size(2), k = a4.size(3);
+  const int64_t nchunks = (seqlen + chunk_size - 1) / chunk_size;
+  const at::ScalarType odt = output_dtype.value_or(a.scalar_type());
+  Tensor out = torch::empty({batch, nchunks, ngroups, chunk_size, chunk_size}, torch::dtype(odt).device(a.device()));
+  ssd_bmm_chunk_params_t p{};
+  p.a = a4.data_ptr();
+  p.b = b4.data_ptr();
+  p.out = out.data_ptr();
+  p.in_dtype = dtype_code(a, "a");
+  p.out_dtype = dtype_code(odt);
+  p.batch = batch;
+  p.seqlen = seqlen;
+  p.ngroups = ngroups;
+  p.k = k;
+  p.chunk_size = chunk_size;
+  p.causal = causal ? 1 : 0;
+  copy_strides(p.a_stride, a4, {0, 1, 2, 3});
+  copy_strides(p.b_stride, b4, {0, 1, 2, 3});
+  copy_strides(p.out_stride, out, {0, 1, 2, 3, 4});
+  Tensor hold;
+  if (seq_idx.has_value()) {
+    check_cuda(*seq_idx, a, "seq_idx");
+    hold = as_int32(*seq_idx);
+    p.seq_idx = hold.data_ptr<int32_t>();
+    p.seq_idx_stride[0] = hold.stride(0);
+    p.seq_idx_stride[1] = hold.stride(1);
+  }
+  check_rc(ssd_bmm_chunk_fwd(&p, current_stream(a)), "ssd_bmm_chunk_fwd");
+  return has_groups ? out : out.squeeze(2);
+}
+
+std::tuple<Tensor, OptTensor> chunk_scan_fwd(const Tensor& cb, const Tensor& x, const Tensor& dt,
+                                             const Tensor& dA_cumsum, const Tensor& C, const Tensor& states,
+                                             const OptTensor& D, const OptTensor& z, const OptTensor& seq_idx) {
+  TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor (libssd_b200 has no CPU path)");
+  for (const Tensor* t : {&cb, &dt, &dA_cumsum, &C, &states}) check_cuda(*t, x, "chunk_scan input");
+  TORCH_CHECK(C.scalar_type() == x.scalar_type(), "C and x must have the same dtype");
+  TORCH_CHECK(dt.scalar_type() == at::kFloat && dA_cumsum.scalar_type() == at::kFloat, "dt and dA_cumsum must be fp32");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x.size(0), x.size(1), x.size(2), x.size(3)}, x.options());
+  OptTensor out_x;
+  ssd_chunk_scan_params_t p{};
+  p.cb = cb.data_ptr();
+  p.x = x.data_ptr();
+  p.dt = dt.data_ptr<float>();
+  p.dA_cumsum = dA_cumsum.data_ptr<float>();
+  p.C = C.data_ptr();
+  p.states = states.data_ptr();
+  p.out = out.data_ptr();
+  p.cb_dtype = dtype_code(cb, "cb");
+  p.in_dtype = dtype_code(x, "x");
+  p.states_dtype = dtype_code(states, "states");
+  p.batch = x.size(0);
+  p.seqlen = x.size(1);
+  p.nheads = x.size(2);
+  p.headdim = x.size(3);
+  p.ngroups = C.size(2);
+  p.dstate = C.size(3);
+  p.chunk_size = dt.size(3);
+  copy_strides(p.cb_stride, cb, {0, 1, 2, 3, 4});
+  copy_strides(p.x_stride, x, {0, 1, 2, 3});
+  copy_strides(p.out_stride, out, {0, 1, 2, 3});
+  copy_strides(p.dt_stride, dt, {0, 1, 2, 3});
+  copy_strides(p.dA_stride, dA_cumsum, {0, 1, 2, 3});
+  copy_strides(p.C_stride, C, {0, 1, 2, 3});
+  copy_strides(p.states_stride, states, {0, 1, 2, 3, 4});
+  Tensor Dh, zh, sh;
+  if (D.has_value()) {
+    check_cuda(*D, x, "D");
+    Dh = D->dim() == 2 && D->stride(1) != 1 ? D->contiguous() : *D;
+    p.D = Dh.data_ptr();
+    p.D_dtype = dtype_code(Dh, "D");
+    p.D_has_hdim = Dh.dim() == 2 ? 1 : 0;
+    p.D_stride = Dh.stride(0);
+  }
+  if (z.has_value()) {
+    check_cuda(*z, x, "z");
+    TORCH_CHECK(z->scalar_type() == x.scalar_type(), "z and x must have the same dtype");
+    zh = *z;
+    p.z = zh.data_ptr();
+    copy_strides(p.z_stride, zh, {0, 1, 2, 3});
+    out_x = torch::empty_like(out);
+    p.out_x = out_x->data_ptr();
+  }
+  if (seq_idx.has_value()) {
+    check_cuda(*seq_idx, x, "seq_idx");
+    sh = as_int32(*seq_idx);
+    p.seq_idx = sh.data_ptr<int32_t>();
+    p.seq_idx_stride[0] = sh.stride(0);
+    p.seq_idx_stride[1] = sh.stride(1);
+  }
+  check_rc(ssd_chunk_scan_fwd(&p, current_stream(x)), "ssd_chunk_scan_fwd");
+  return {out, out_x};
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "PyTorch front end of libssd_b200 (Mamba2 SSD forward hot path on sm_100a)";
+  m.def("abi_version", []() { return ssd_abi_version(); });
+  m.def("chunk_cumsum_fwd", &chunk_cumsum_fwd, py::arg("dt"), py::arg("A"), py::arg("chunk_size"),
+        py::arg("dt_bias") = py::none(), py::arg("dt_softplus") = false, py::arg("dt_min") = 0.0,
+        py::arg("dt_max") = std::numeric_limits<double>::infinity());
+  m.def("chunk_state_fwd", &chunk_state_fwd, py::arg("B"), py::arg("x"), py::arg("dt"), py::arg("dA_cumsum"),
+        py::arg("seq_idx") = py::none(), py::arg("states") = py::none(), py::arg("states_in_fp32") = true);
+  m.def("state_passing_fwd", &state_passing_fwd, py::arg("states"), py::arg("dA_chunk_cumsum"),
+        py::arg("initial_states") = py::none(), py::arg("seq_idx") = py::none(), py::arg("chunk_size") = 0,
+        py::arg("out_dtype") = py::none());
+  m.def("fused_state_fwd", &fused_state_fwd, py::arg("B"), py::arg("x"), py::arg("dt"), py::arg("dA_cumsum"),
+        py::arg("out_dtype") = py::none(), py::arg("initial_states") = py::none(), py::arg("seq_idx") = py::none(),
+        py::arg("states") = py::none(), py::arg("states_in_fp32") = true, py::arg("clamp_decay") = true,
+        py::arg("force_general") = false);
+  m.def("check_status", &check_status, py::arg("like"));
+  m.def("bmm_chunk_fwd", &bmm_chunk_fwd, py::arg("a"), py::arg("b"), py::arg("chunk_size"),
+        py::arg("seq_idx") = py::none(), py::arg("causal") = false, py::arg("output_dtype") = py::none());
+  m.def("chunk_scan_fwd", &chunk_scan_fwd, py::arg("cb"), py::arg("x"), py::arg("dt"), py::arg("dA_cumsum"),
+        py::arg("C"), py::arg("states"), py::arg("D") = py::none(), py::arg("z") = py::none(),
+        py::arg("seq_idx") = py::none());
+}
