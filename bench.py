@@ -138,21 +138,25 @@ def cpu_hot_path(sample_batch, threads, reps):
     inp = O.make_inputs(w["batch"], w["seqlen"], w["nheads"], w["headdim"], w["ngroups"], w["dstate"],
                         dtype=torch.bfloat16, seed=0)
     times = []
-    for _ in range(reps + 1):
+    budget_s = 15.0
+    while True:
         t0 = time.perf_counter()
         O.hot_path_fwd(inp["x"], inp["dt"], inp["A"], inp["B"], w["chunk_size"], dt_bias=inp["dt_bias"],
                        dt_softplus=True, out_dtype=torch.bfloat16)
         times.append(time.perf_counter() - t0)
-    t = statistics.median(times[1:])           # first pass warms the allocator
-    return w["batch"] * w["seqlen"] / t, t
+        # first pass warms the allocator; then `reps` timed passes, cut short at ~15 s of work
+        if len(times) > reps or (len(times) >= 3 and sum(times) > budget_s):
+            break
+    t = statistics.median(times[1:])
+    return w["batch"] * w["seqlen"] / t, t, len(times) - 1
 
 
 def run_reference_arm(args, rank, world):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    sample_batch = 1
-    tok_s, t = cpu_hot_path(sample_batch, threads, max(1, min(args.steps, 3)))
+    sample_batch = WORKLOAD["batch"]
+    tok_s, t, n = cpu_hot_path(sample_batch, threads, max(2, min(args.steps, 20)))
     line = {
         "impl": "reference", "metric": "ssd_state_path_tokens_per_s", "value": tok_s, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
@@ -160,8 +164,8 @@ def run_reference_arm(args, rank, world):
         "config": dict(workload=WORKLOAD["name"], **{k: v for k, v in WORKLOAD.items() if k != "name"},
                        parallelism="host threads"),
         "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": f"batch {sample_batch} of {WORKLOAD['batch']} of the workload per step "
-                                   f"(same seqlen, heads, dims); torch chunked SSD math, bf16 inputs"},
+                         "sample": f"the whole workload per step, {n} timed passes ({t:.2f} s each, median); "
+                                   f"torch chunked SSD math, bf16 inputs"},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -175,6 +179,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true", help="profiling aid: device-resident timing only")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="profiling aid: override the workload's batch (the bench line then names it)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -198,7 +205,10 @@ def main():
     from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
     from mamba_fused_minimal_b200.kernels.ssd_chunk_state import _chunk_cumsum_fwd as cumsum
 
-    w = WORKLOAD
+    w = dict(WORKLOAD)
+    if args.batch is not None:
+        w["batch"] = args.batch
+        w["name"] = f"{WORKLOAD['name']}-batch{args.batch}"
     L = w["chunk_size"]
     # every rank: its own shard of 80 heads (seeded by rank), no data shared between ranks
     d = generate_benchmark_data(w["batch"], w["seqlen"], w["nheads"], w["headdim"], w["ngroups"], w["dstate"],
@@ -243,42 +253,44 @@ def main():
     from mamba_fused_minimal_b200._ext import C as _C
     _C.check_status(x)
 
-    # ---- end to end from pinned host buffers --------------------------------------------
-    hx, hB, hdt = (t.cpu().pin_memory() for t in (x, B, dt))
-    hA, hbias = A.cpu().pin_memory(), bias.cpu().pin_memory()
-    nchunks = (w["seqlen"] + L - 1) // L
-    h_out = torch.empty((w["batch"], nchunks, w["nheads"], w["headdim"], w["dstate"]), dtype=torch.bfloat16).pin_memory()
-    h_fin = torch.empty((w["batch"], w["nheads"], w["headdim"], w["dstate"]), dtype=torch.float32).pin_memory()
-    h_dA = torch.empty((w["batch"], w["nheads"], nchunks, L), dtype=torch.float32).pin_memory()
-    h_dt = torch.empty_like(h_dA).pin_memory()
-    dx, dB, ddt, dA_, dbias = (torch.empty_like(t) for t in (x, B, dt, A, bias))
-    h2d = sum(t.numel() * t.element_size() for t in (hx, hB, hdt, hA, hbias))
-    d2h = sum(t.numel() * t.element_size() for t in (h_out, h_fin, h_dA, h_dt))
+    e2e_ms, h2d, d2h, Ke = float('nan'), 0, 0, 0
+    if not args.skip_e2e:
+        # ---- end to end from pinned host buffers --------------------------------------------
+        hx, hB, hdt = (t.cpu().pin_memory() for t in (x, B, dt))
+        hA, hbias = A.cpu().pin_memory(), bias.cpu().pin_memory()
+        nchunks = (w["seqlen"] + L - 1) // L
+        h_out = torch.empty((w["batch"], nchunks, w["nheads"], w["headdim"], w["dstate"]), dtype=torch.bfloat16).pin_memory()
+        h_fin = torch.empty((w["batch"], w["nheads"], w["headdim"], w["dstate"]), dtype=torch.float32).pin_memory()
+        h_dA = torch.empty((w["batch"], w["nheads"], nchunks, L), dtype=torch.float32).pin_memory()
+        h_dt = torch.empty_like(h_dA).pin_memory()
+        dx, dB, ddt, dA_, dbias = (torch.empty_like(t) for t in (x, B, dt, A, bias))
+        h2d = sum(t.numel() * t.element_size() for t in (hx, hB, hdt, hA, hbias))
+        d2h = sum(t.numel() * t.element_size() for t in (h_out, h_fin, h_dA, h_dt))
 
-    def e2e_step():
-        dx.copy_(hx, non_blocking=True)
-        dB.copy_(hB, non_blocking=True)
-        ddt.copy_(hdt, non_blocking=True)
-        dA_.copy_(hA, non_blocking=True)
-        dbias.copy_(hbias, non_blocking=True)
-        a, t_ = cumsum(ddt, dA_, L, dt_bias=dbias, dt_softplus=True)
-        o, f = fused(dB, dx, t_, a, torch.bfloat16)
-        h_out.copy_(o, non_blocking=True)
-        h_fin.copy_(f, non_blocking=True)
-        h_dA.copy_(a, non_blocking=True)
-        h_dt.copy_(t_, non_blocking=True)
+        def e2e_step():
+            dx.copy_(hx, non_blocking=True)
+            dB.copy_(hB, non_blocking=True)
+            ddt.copy_(hdt, non_blocking=True)
+            dA_.copy_(hA, non_blocking=True)
+            dbias.copy_(hbias, non_blocking=True)
+            a, t_ = cumsum(ddt, dA_, L, dt_bias=dbias, dt_softplus=True)
+            o, f = fused(dB, dx, t_, a, torch.bfloat16)
+            h_out.copy_(o, non_blocking=True)
+            h_fin.copy_(f, non_blocking=True)
+            h_dA.copy_(a, non_blocking=True)
+            h_dt.copy_(t_, non_blocking=True)
 
-    Ke = max(3, min(K, 20))
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(Ke):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / Ke
+        Ke = max(3, min(K, 20))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(Ke):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / Ke
     clocks = sampler.stop() if sampler is not None else None
 
     # ---- max over ranks ---------------------------------------------------------------
@@ -315,10 +327,10 @@ def main():
         }
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
-            tok_s, t = cpu_hot_path(1, threads, 2)
+            tok_s, t, n = cpu_hot_path(WORKLOAD["batch"], threads, 20)
             line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                    "sample": "batch 1 of 8 of the workload, 2 timed passes "
-                                              f"({t:.2f} s each); torch chunked SSD math on the host"}
+                                    "sample": f"the whole workload, {n} timed passes ({t:.2f} s each, median); "
+                                              "torch chunked SSD math on the host"}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

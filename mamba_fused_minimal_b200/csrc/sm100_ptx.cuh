@@ -222,14 +222,6 @@ __host__ __device__ constexpr uint32_t mma_idesc(uint32_t fmt, bool a_mn_major, 
          ((b_mn_major ? 1u : 0u) << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// exp(x) the way a fast-math exponential evaluates it: 2^(x * log2 e).
-__device__ __forceinline__ float fast_exp(float x) { return ex2_approx(x * 1.4426950408889634f); }
-
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

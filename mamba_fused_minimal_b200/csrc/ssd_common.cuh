@@ -65,6 +65,16 @@ __device__ __forceinline__ float round_to(float v, int dtype) {
   }
 }
 
+// exp(x) evaluated as 2^(x * log2 e) with the hardware ex2 approximation: the form a
+// compiled Triton `tl.exp` takes on NVIDIA GPUs, so decay factors computed here carry the
+// same bits as the reference's.  Every kernel of the library uses this one function for the
+// decay terms, which keeps the fused and the unfused routes bit-identical to each other.
+__device__ __forceinline__ float fast_exp(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+
 // log(exp(x) + 1) where x <= 20, x otherwise: the reference's softplus
 // (kernels/softplus.py:8-10 applied at kernels/ssd_chunk_state.py:70).
 __device__ __forceinline__ float softplus_ref(float x) {

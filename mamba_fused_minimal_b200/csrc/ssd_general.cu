@@ -118,7 +118,7 @@ state_passing_kernel(ssd_state_passing_params_t p) {
     if (c + 1 < p.nchunks)
       nxt = load_f(p.states, p.states_dtype, sbase + (int64_t)(c + 1) * p.states_stride[1]);
     store_f(p.out, p.out_dtype, obase + (int64_t)c * p.out_stride[1], s);
-    float scale = expf(load_f(p.dA_chunk_cumsum, p.dA_dtype, abase + (int64_t)c * p.dA_stride[2]));
+    float scale = fast_exp(load_f(p.dA_chunk_cumsum, p.dA_dtype, abase + (int64_t)c * p.dA_stride[2]));
     if (p.seq_idx != nullptr) {
       const int pos = min((c + 1) * p.chunk_size, p.seqlen) - 1;
       const int seq_new = p.seq_idx[(int64_t)b * p.seq_idx_stride[0] + (int64_t)pos * p.seq_idx_stride[1]];
@@ -258,7 +258,7 @@ struct ChunkStateProblem {
       if (k < c.limit) {
         float d = last - in.dA_cumsum[dab + (int64_t)k * in.dA_stride[3]];
         if (clamp_decay) d = fminf(d, 0.0f);
-        s = expf(d) * in.dt[dtb + (int64_t)k * in.dt_stride[3]];
+        s = fast_exp(d) * in.dt[dtb + (int64_t)k * in.dt_stride[3]];
         if (in.seq_idx && in.seq_idx[sib + (int64_t)k * in.seq_idx_stride[1]] != seq_last) s = 0.0f;
       }
       vec0[k] = s;
@@ -416,7 +416,7 @@ struct ChunkScanProblem {
     }
     if (m >= p.chunk_size || k > m) return 0.0f;
     float v = load_f(p.cb, p.cb_dtype, c.cbbase + (int64_t)m * p.cb_stride[3] + (int64_t)k * p.cb_stride[4]);
-    v *= expf(fminf(c.dA[m] - c.dA[k], 0.0f));
+    v *= fast_exp(fminf(c.dA[m] - c.dA[k], 0.0f));
     v *= c.dt[k];
     return round_to(v, p.in_dtype);
   }
@@ -430,7 +430,7 @@ struct ChunkScanProblem {
   }
   __device__ float after_phase(const Ctx& c, int phase, int m, float acc) const {
     if (phase != 0 || m >= p.chunk_size) return acc;
-    float s = expf(c.dA[m]);
+    float s = fast_exp(c.dA[m]);
     if (p.seq_idx) {
       const int sm = m < c.limit ? p.seq_idx[c.sib + (int64_t)m * p.seq_idx_stride[1]] : -1;
       if (sm != c.seq_prev) s = 0.0f;

@@ -44,6 +44,21 @@ def _pad_seq(t, chunk_size, dim=1):
     return torch.cat([t, torch.zeros(shape, dtype=t.dtype)], dim=dim)
 
 
+LOG2E_F32 = 1.4426950408889634
+
+
+def _exp(x, impl="exact"):
+    """exp(x) in fp32.  "exact": torch.exp (what the Triton interpreter computes).  "ex2":
+    2^(fl32(x * log2 e)), the form `tl.exp` compiles to on NVIDIA GPUs -- the rounding of the
+    product to fp32 is what distinguishes the two (up to a few 1e-6 relative for |x| ~ 100),
+    enough to flip the 16-bit rounding of a scaled B element now and then."""
+    x = x.float()
+    if impl == "exact":
+        return torch.exp(x)
+    assert impl == "ex2"
+    return torch.exp2(x * torch.tensor(LOG2E_F32, dtype=torch.float32))
+
+
 def softplus_ref(x):
     """kernels/softplus.py:8-10 (Triton >= 3 form): log(exp(x) + 1)."""
     return torch.log(torch.exp(x) + 1.0)
@@ -82,7 +97,7 @@ def _chunked(t, chunk_size):
 
 
 def chunk_state_fwd(B, x, dt, dA_cumsum, seq_idx=None, states=None, states_in_fp32=True,
-                    clamp_decay=True):
+                    clamp_decay=True, exp_impl="exact"):
     """Per-chunk states (batch, nchunks, nheads, headdim, dstate).
 
     states[p, n] = sum_k x[k, p] * cast(B[k, n] * exp(min(dA_last - dA_k, 0)) * dt_k),
@@ -105,7 +120,7 @@ def chunk_state_fwd(B, x, dt, dA_cumsum, seq_idx=None, states=None, states_in_fp
     expo = dA[..., -1:] - dA                                  # b h c k
     if clamp_decay:
         expo = torch.clamp(expo, max=0.0)
-    scale = torch.exp(expo) * dt.float()                      # b h c k
+    scale = _exp(expo, exp_impl) * dt.float()                 # b h c k
     if seq_idx is not None:
         assert seq_idx.shape == (batch, seqlen)
         sic = _chunked(seq_idx.to(torch.int64) + 1, chunk_size) - 1     # pad = -1
@@ -124,7 +139,7 @@ def chunk_state_fwd(B, x, dt, dA_cumsum, seq_idx=None, states=None, states_in_fp
 
 
 def state_passing_fwd(states, dA_chunk_cumsum, initial_states=None, seq_idx=None,
-                      chunk_size=None, out_dtype=None):
+                      chunk_size=None, out_dtype=None, exp_impl="exact"):
     """Exclusive scan of the chunk states (kernels/ssd_state_passing.py:61-84).
 
     states (batch, nchunks, nheads, dim); dA_chunk_cumsum (batch, nheads, nchunks).
@@ -146,7 +161,7 @@ def state_passing_fwd(states, dA_chunk_cumsum, initial_states=None, seq_idx=None
         prev = torch.zeros(batch, dtype=torch.int64)
     for c in range(nchunks):
         out[:, c] = s.to(out_dtype)
-        scale = torch.exp(dA_chunk_cumsum[:, :, c].float())              # b h
+        scale = _exp(dA_chunk_cumsum[:, :, c], exp_impl)                 # b h
         if seq_idx is not None:
             new = seq_idx[:, min((c + 1) * chunk_size, seqlen) - 1].to(torch.int64)
             scale = torch.where((new == prev)[:, None], scale, torch.zeros_like(scale))
@@ -156,7 +171,7 @@ def state_passing_fwd(states, dA_chunk_cumsum, initial_states=None, seq_idx=None
 
 
 def fused_state_fwd(B, x, dt, dA_cumsum, out_dtype, initial_states=None, seq_idx=None,
-                    states=None, states_in_fp32=True):
+                    states=None, states_in_fp32=True, exp_impl="exact"):
     """What both fused entry points return: (out (b,c,h,p,n) out_dtype, final (b,h,p,n) fp32).
 
     Composition of the two functions above (that composition is what the reference's own
@@ -164,13 +179,14 @@ def fused_state_fwd(B, x, dt, dA_cumsum, out_dtype, initial_states=None, seq_idx
     (kernels/fused_concurrent.py:277).
     """
     st = chunk_state_fwd(B, x, dt, dA_cumsum, seq_idx=seq_idx, states=states,
-                         states_in_fp32=states_in_fp32)
+                         states_in_fp32=states_in_fp32, exp_impl=exp_impl)
     b, c, h, p, n = st.shape
     chunk_size = dt.shape[-1]
     init = None if initial_states is None else initial_states.reshape(b, h, p * n)
     out, fin = state_passing_fwd(st.reshape(b, c, h, p * n), dA_cumsum[:, :, :, -1],
                                  initial_states=init, seq_idx=seq_idx, chunk_size=chunk_size,
-                                 out_dtype=st.dtype if out_dtype is None else out_dtype)
+                                 out_dtype=st.dtype if out_dtype is None else out_dtype,
+                                 exp_impl=exp_impl)
     return out.view(b, c, h, p, n), fin.view(b, h, p, n)
 
 
@@ -204,7 +220,8 @@ def bmm_chunk_fwd(a, b, chunk_size, seq_idx=None, causal=False, output_dtype=Non
     return out if has_groups else out[:, :, 0]
 
 
-def chunk_scan_fwd(cb, x, dt, dA_cumsum, C, states, D=None, z=None, seq_idx=None):
+def chunk_scan_fwd(cb, x, dt, dA_cumsum, C, states, D=None, z=None, seq_idx=None,
+                   exp_impl="exact"):
     """Returns (out, out_x) (kernels/ssd_chunk_scan.py:83-169).
 
     out[m] = exp(dA_m) * C[m] . cast(prev_state)  +  sum_{k<=m} cast(cb[m,k] *
@@ -222,7 +239,7 @@ def chunk_scan_fwd(cb, x, dt, dA_cumsum, C, states, D=None, z=None, seq_idx=None
     xc = _chunked(x, L)                                                # b c k h p
     Cc = _chunked(C, L).repeat_interleave(ratio, dim=3)                # b c m h n
     dA = dA_cumsum.float()                                             # b h c L
-    scale_m = torch.exp(dA)                                            # b h c m
+    scale_m = _exp(dA, exp_impl)                                       # b h c m
     if seq_idx is not None:
         sic = _chunked(seq_idx.to(torch.int64) + 1, L) - 1             # b c m, pad -1
         prev = torch.zeros(batch, nchunks, dtype=torch.int64)
@@ -235,7 +252,7 @@ def chunk_scan_fwd(cb, x, dt, dA_cumsum, C, states, D=None, z=None, seq_idx=None
     acc = acc * scale_m.permute(0, 2, 3, 1)[..., None]
     cbh = cb.float().repeat_interleave(ratio, dim=2)                   # b c h m k
     seg = torch.clamp(dA[..., :, None] - dA[..., None, :], max=0.0)    # b h c m k
-    w = cbh * torch.exp(seg).permute(0, 2, 1, 3, 4)
+    w = cbh * _exp(seg, exp_impl).permute(0, 2, 1, 3, 4)
     w = w * dt.float().permute(0, 2, 1, 3)[:, :, :, None, :]
     causal = torch.tril(torch.ones(L, L, dtype=torch.bool))
     w = torch.where(causal, w, torch.zeros_like(w)).to(x.dtype)        # rounding point
@@ -254,27 +271,30 @@ def chunk_scan_fwd(cb, x, dt, dA_cumsum, C, states, D=None, z=None, seq_idx=None
 
 
 def combined_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None,
-                 initial_states=None, dt_softplus=False, dt_limit=(0.0, float("inf"))):
+                 initial_states=None, dt_softplus=False, dt_limit=(0.0, float("inf")),
+                 exp_impl="exact"):
     """The reference's unfused pipeline, main.py:60-74.  Returns the same 6-tuple
     (out, out_x, dt, dA_cumsum, states, final_states)."""
     dA_cumsum, dt_out = chunk_cumsum_fwd(dt, A, chunk_size, dt_bias=dt_bias,
                                          dt_softplus=dt_softplus, dt_limit=dt_limit)
     states, final_states = fused_state_fwd(B, x, dt_out, dA_cumsum, C.dtype,
-                                           initial_states=initial_states)
+                                           initial_states=initial_states, exp_impl=exp_impl)
     CB = bmm_chunk_fwd(C, B, chunk_size, output_dtype=torch.float32)
-    out, out_x = chunk_scan_fwd(CB, x, dt_out, dA_cumsum, C, states, D=D, z=z)
+    out, out_x = chunk_scan_fwd(CB, x, dt_out, dA_cumsum, C, states, D=D, z=z,
+                                exp_impl=exp_impl)
     return out, out_x, dt_out, dA_cumsum, states, final_states
 
 
 def hot_path_fwd(x, dt, A, B, chunk_size, dt_bias=None, dt_softplus=False,
-                 dt_limit=(0.0, float("inf")), out_dtype=None, initial_states=None):
+                 dt_limit=(0.0, float("inf")), out_dtype=None, initial_states=None,
+                 exp_impl="exact"):
     """cumsum -> chunk state -> state passing: the timed path.  Returns
     (dA_cumsum, dt_out, out, final_states)."""
     dA_cumsum, dt_out = chunk_cumsum_fwd(dt, A, chunk_size, dt_bias=dt_bias,
                                          dt_softplus=dt_softplus, dt_limit=dt_limit)
     out, fin = fused_state_fwd(B, x, dt_out, dA_cumsum,
                                B.dtype if out_dtype is None else out_dtype,
-                               initial_states=initial_states)
+                               initial_states=initial_states, exp_impl=exp_impl)
     return dA_cumsum, dt_out, out, fin
 
 
