@@ -63,10 +63,14 @@ struct WaitCtx {
   int* status;                // global memory, one per launch
 };
 
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx w, int code) {
+// `sleep_ns` > 0 makes the waiter back off between polls: for roles that wait long and are
+// not on the critical path, so that their polling does not take issue slots from the rest.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx w, int code,
+                                            uint32_t sleep_ns) {
   const uint64_t t0 = globaltimer_ns();
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if ((++it & 127u) == 0) {
       if (*w.abort_flag) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
@@ -78,9 +82,10 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitC
   }
   return true;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtx w, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtx w, int code,
+                                          uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, w, code);
+  return mbar_wait_slow(bar, parity, w, code, sleep_ns);
 }
 
 // Wait until *flag == target (written by another CTA with release semantics).

@@ -49,7 +49,7 @@ enum WaitCode {
 template <int HPC>
 struct Cfg {
   static constexpr int NS = (HPC == 1) ? 5 : 4;       // TMA stages
-  static constexpr int NT = 4;                        // scaled-B tiles
+  static constexpr int NT = (HPC == 1) ? 3 : 2;       // scaled-B slots (one tile per head each)
   static constexpr int ND = 2;                        // dt/dA row slots
   static constexpr int NBUF = 4;                      // TMEM accumulators per head
   static constexpr int EPI_WARPS = 4 * HPC;
@@ -64,7 +64,8 @@ struct Cfg {
   // shared-memory map (byte offsets from a 1024-aligned base)
   static constexpr int OFF_STAGES = 0;
   static constexpr int OFF_BS = OFF_STAGES + NS * STAGE_BYTES;
-  static constexpr int OFF_DTDA = OFF_BS + NT * RAWB_BYTES;
+  static constexpr int BS_SLOT = HPC * RAWB_BYTES;
+  static constexpr int OFF_DTDA = OFF_BS + NT * BS_SLOT;
   static constexpr int DTDA_SLOT = HPC * 2 * kMaxL * 4;
   static constexpr int OFF_SCALE = OFF_DTDA + ND * DTDA_SLOT;
   static constexpr int SCALE_SLOT = HPC * kMaxL * 4;
@@ -295,7 +296,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ============================== MMA issuer ========================================
     if (lane == 0) {
       constexpr uint32_t idesc = mma_idesc(Pack<T>::kFmt, true, true, kN, kP);
-      uint32_t it = 0, item = 0, tcount = 0;
+      uint32_t it = 0, item = 0;
       bool ok = true;
       for (int j = 0; j < rg.m && ok; ++j) {
         int strip, c0, c1;
@@ -315,13 +316,13 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
             ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
             if (!ok) break;
             const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
+            const int t = it % C::NT;
+            ok = mbar_wait(bar_bs_full(t), (it / C::NT) & 1, wc, kWaitBsFull);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
             for (int hd = 0; hd < HPC; ++hd) {
-              const int t = tcount % C::NT;
-              ok = mbar_wait(bar_bs_full(t), (tcount / C::NT) & 1, wc, kWaitBsFull);
-              if (!ok) break;
-              tc_fence_after();
-              const uint32_t a_base = sbase + C::OFF_BS + t * C::RAWB_BYTES;
+              const uint32_t a_base = sbase + C::OFF_BS + t * C::BS_SLOT + hd * C::RAWB_BYTES;
               const uint32_t b_base = st + C::RAWB_BYTES + hd * C::X_BYTES;
               const uint32_t d_tmem = tmem_base + (hd * C::NBUF + buf) * kP;
 #pragma unroll
@@ -330,9 +331,8 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 const uint64_t bd = smem_desc_sw128(b_base + k16 * 2048, C::X_BYTES, 1024);
                 mma_f16_ss(d_tmem, ad, bd, idesc, (ks | k16) != 0 ? 1u : 0u);
               }
-              mma_commit(bar_bs_empty(t));
-              ++tcount;
             }
+            mma_commit(bar_bs_empty(t));
             if (ok) mma_commit(bar_empty(s));
           }
           if (ok) mma_commit(bar_acc_full(buf));
@@ -342,7 +342,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else if (warp >= C::EPI_WARPS + 2) {
     // ============================== B scaling =========================================
     const int stid = tid - (C::EPI_WARPS + 2) * 32;
-    uint32_t it = 0, item = 0, tcount = 0;
+    uint32_t it = 0, item = 0;
     bool ok = true;
     for (int j = 0; j < rg.m && ok; ++j) {
       int strip, c0, c1;
@@ -371,31 +371,52 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
           ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
           if (!ok) break;
           const uint8_t* raw = smem + C::OFF_STAGES + s * C::STAGE_BYTES;
+          const int t = it % C::NT;
+          ok = mbar_wait(bar_bs_empty(t), ((it / C::NT) & 1) ^ 1, wc, kWaitBsEmpty);
+          if (!ok) break;
+          uint8_t* dst = smem + C::OFF_BS + t * C::BS_SLOT;
+          const float* sch = sc + ks * kKT;
+          // One pass over the raw B tile produces the scaled tile of every head of the CTA.
+          // All loads of a thread are issued before the first use, so the shared-memory
+          // latency is paid once per stage rather than once per 16 bytes.
+          constexpr int kChunks = C::RAWB_BYTES / 16;
+          constexpr int kPerThread = (kChunks + C::SCALE_THREADS - 1) / C::SCALE_THREADS;
+          uint4 v[kPerThread];
 #pragma unroll
-          for (int hd = 0; hd < HPC; ++hd) {
-            const int t = tcount % C::NT;
-            ok = mbar_wait(bar_bs_empty(t), ((tcount / C::NT) & 1) ^ 1, wc, kWaitBsEmpty);
-            if (!ok) break;
-            uint8_t* dst = smem + C::OFF_BS + t * C::RAWB_BYTES;
-            const float* sch = sc + hd * kMaxL + ks * kKT;
-            for (int i = stid; i < C::RAWB_BYTES / 16; i += C::SCALE_THREADS) {
+          for (int q = 0; q < kPerThread; ++q) {
+            const int i = stid + q * C::SCALE_THREADS;
+            if (kChunks % C::SCALE_THREADS == 0 || i < kChunks)
+              v[q] = *reinterpret_cast<const uint4*>(raw + i * 16);
+          }
+#pragma unroll
+          for (int q = 0; q < kPerThread; ++q) {
+            const int i = stid + q * C::SCALE_THREADS;
+            if (kChunks % C::SCALE_THREADS == 0 || i < kChunks) {
               const int off = i * 16;
               const int row = (off & (C::RAWB_BYTES / 2 - 1)) >> 7;      // k within the stage
-              const float f = sch[row];
-              const uint4 v = *reinterpret_cast<const uint4*>(raw + off);
-              uint4 o;
-              float lo, hi;
-              Pack<T>::unpack(v.x, lo, hi); o.x = Pack<T>::pack(lo * f, hi * f);
-              Pack<T>::unpack(v.y, lo, hi); o.y = Pack<T>::pack(lo * f, hi * f);
-              Pack<T>::unpack(v.z, lo, hi); o.z = Pack<T>::pack(lo * f, hi * f);
-              Pack<T>::unpack(v.w, lo, hi); o.w = Pack<T>::pack(lo * f, hi * f);
-              *reinterpret_cast<uint4*>(dst + off) = o;
+              float2 e0, e1, e2, e3;
+              Pack<T>::unpack(v[q].x, e0.x, e0.y);
+              Pack<T>::unpack(v[q].y, e1.x, e1.y);
+              Pack<T>::unpack(v[q].z, e2.x, e2.y);
+              Pack<T>::unpack(v[q].w, e3.x, e3.y);
+#pragma unroll
+              for (int hd = 0; hd < HPC; ++hd) {
+                const float f = sch[hd * kMaxL + row];
+                const float2 ff = make_float2(f, f);
+                const float2 r0 = __fmul2_rn(e0, ff), r1 = __fmul2_rn(e1, ff);
+                const float2 r2 = __fmul2_rn(e2, ff), r3 = __fmul2_rn(e3, ff);
+                uint4 o;
+                o.x = Pack<T>::pack(r0.x, r0.y);
+                o.y = Pack<T>::pack(r1.x, r1.y);
+                o.z = Pack<T>::pack(r2.x, r2.y);
+                o.w = Pack<T>::pack(r3.x, r3.y);
+                *reinterpret_cast<uint4*>(dst + hd * C::RAWB_BYTES + off) = o;
+              }
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_bs_full(t));
-            ++tcount;
           }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_bs_full(t));
         }
       }
     }
@@ -436,7 +457,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
         float decay = 0.0f;
         if (a.mode == 0)
           decay = fast_exp(__ldg(a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2] + (L - 1)));
-        ok = mbar_wait(bar_acc_full(buf), (item / C::NBUF) & 1, wc, kWaitAccFull);
+        ok = mbar_wait(bar_acc_full(buf), (item / C::NBUF) & 1, wc, kWaitAccFull, 128);
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + lane_sel + (hd * C::NBUF + buf) * kP;

@@ -32,19 +32,35 @@ chunk_cumsum_kernel(ssd_chunk_cumsum_params_t p, int nchunks) {
   const int limit = min(L, p.seqlen - c * L);
   const int tid = threadIdx.x;
 
-  for (int i = tid; i < L * CS_HT; i += CS_THREADS) {
-    const int k = i / CS_HT, hh = i % CS_HT;
-    const int h = h0 + hh;
-    float v = 0.0f;
-    if (h < p.nheads && k < limit) {
-      v = load_f(p.dt, p.dt_dtype,
-                 (int64_t)b * p.dt_stride_b + (int64_t)(c * L + k) * p.dt_stride_l +
-                     (int64_t)h * p.dt_stride_h);
-      if (p.dt_bias != nullptr) v += load_f(p.dt_bias, p.bias_dtype, (int64_t)h * p.bias_stride);
-      if (p.dt_softplus) v = softplus_ref(v);
-      v = fminf(fmaxf(v, p.dt_min), p.dt_max);
+  // a thread always serves the same head (CS_THREADS is a multiple of CS_HT)
+  const int hh_t = tid % CS_HT;
+  const int h_t = h0 + hh_t;
+  const bool head_ok = h_t < p.nheads;
+  const float bias = (head_ok && p.dt_bias != nullptr)
+                         ? load_f(p.dt_bias, p.bias_dtype, (int64_t)h_t * p.bias_stride) : 0.0f;
+  const int64_t dt_base = (int64_t)b * p.dt_stride_b + (int64_t)c * L * p.dt_stride_l + (int64_t)h_t * p.dt_stride_h;
+  constexpr int kRowsPerPass = CS_THREADS / CS_HT;     // 16 positions per pass
+  constexpr int kUnroll = 8;                           // loads in flight per thread
+  for (int k0 = tid / CS_HT; k0 < L; k0 += kRowsPerPass * kUnroll) {
+    float v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int k = k0 + u * kRowsPerPass;
+      v[u] = (head_ok && k < limit) ? load_f(p.dt, p.dt_dtype, dt_base + (int64_t)k * p.dt_stride_l) : 0.0f;
     }
-    tile[k * (CS_HT + 1) + hh] = v;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int k = k0 + u * kRowsPerPass;
+      if (k < L) {
+        float t = 0.0f;
+        if (head_ok && k < limit) {
+          t = v[u] + bias;
+          if (p.dt_softplus) t = softplus_ref(t);
+          t = fminf(fmaxf(t, p.dt_min), p.dt_max);
+        }
+        tile[k * (CS_HT + 1) + hh_t] = t;
+      }
+    }
   }
   __syncthreads();
 
