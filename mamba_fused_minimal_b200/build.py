@@ -71,7 +71,7 @@ def _run(cmd, verbose):
 def build_lib(force=False, verbose=False):
     srcs = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
     hdrs = [h if os.path.isabs(h) else os.path.join(CSRC, h) for h in CUDA_HEADERS]
-    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + os.environ.get("SSD_EXTRA_NVCC_FLAGS", "").split()
     stamp = _digest(srcs + hdrs, " ".join(flags))
     if not force and not _stale(LIB, stamp):
         return LIB

@@ -32,12 +32,31 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+#ifndef SSD_SUSPEND_HINT_NS
+#define SSD_SUSPEND_HINT_NS 20000
+#endif
+// One potentially-blocking probe: the hardware may park the thread until the phase
+// completes or the suspend-time hint (nanoseconds) runs out, so a long wait costs a
+// handful of instructions instead of a spin loop's worth.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       " .reg .pred p;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"((uint32_t)SSD_SUSPEND_HINT_NS)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
       " selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -53,10 +72,12 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// Every device-side wait in this library is bounded: after kWaitLimitNs without progress
-// the waiter raises the CTA's abort flag, records `code` in the global status word and
-// returns false; every other waiter in the CTA sees the flag and returns false too.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
+// Every device-side wait in this library is bounded: after kWaitLimitCycles SM clocks
+// (about two seconds) without progress the waiter raises the CTA's abort flag, records
+// `code` in the global status word and returns false; every other waiter in the CTA sees
+// the flag and returns false too.  The limit is measured with the SM's own cycle counter,
+// which costs a few cycles to read, and only consulted once per 256 polls.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 struct WaitCtx {
   volatile int* abort_flag;   // shared memory, one per CTA
@@ -67,13 +88,15 @@ struct WaitCtx {
 // not on the critical path, so that their polling does not take issue slots from the rest.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx w, int code,
                                             uint32_t sleep_ns) {
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
     if (sleep_ns) __nanosleep(sleep_ns);
-    if ((++it & 127u) == 0) {
+    if ((++it & 255u) == 0) {
       if (*w.abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitCycles) {
         *w.abort_flag = 1;
         atomicCAS(w.status, 0, code);
         return false;
@@ -99,13 +122,15 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
 }
 __device__ __noinline__ bool flag_wait(const uint32_t* flag, uint32_t target, WaitCtx w, int code) {
   if (ld_acquire_gpu(flag) == target) return true;
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t it = 0;
   while (ld_acquire_gpu(flag) != target) {
     __nanosleep(64);
-    if ((++it & 31u) == 0) {
+    if ((++it & 63u) == 0) {
       if (*w.abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitCycles) {
         *w.abort_flag = 1;
         atomicCAS(w.status, 0, code);
         return false;
@@ -138,6 +163,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
       : "memory");
+}
+// 16-byte asynchronous copy global -> shared by the calling thread; src_bytes = 0 zero-fills.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -194,6 +228,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }

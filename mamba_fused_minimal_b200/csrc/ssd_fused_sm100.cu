@@ -223,8 +223,9 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(bar_acc_full(b), 1);
       for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_acc_empty(hd, b), 4);
     }
-    mbar_init(bar_sc_sync(), C::SCALE_THREADS);
-    for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_epi_sync(hd), 128);
+    // group barriers take ONE arrival per warp: arrivals on one mbarrier serialise
+    mbar_init(bar_sc_sync(), C::SCALE_WARPS);
+    for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_epi_sync(hd), 4);
     ctl[0] = 0;
     ctl[2] = reinterpret_cast<volatile int*>(a.status)[1];     // epoch of the previous launch
     fence_barrier_init();
@@ -360,7 +361,8 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (a.clamp_decay) d = fminf(d, 0.0f);
           sc[hd * kMaxL + k] = fast_exp(d) * row[k];
         }
-        mbar_arrive(bar_sc_sync());
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sc_sync());
         ok = mbar_wait(bar_sc_sync(), item & 1, wc, kWaitGroup);
         if (!ok) break;
         if (stid == 0) mbar_arrive(bar_dd_empty(r));
@@ -501,7 +503,8 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
         for (int p = 0; p < kP; ++p) __stcg(co + p * kN, S[p]);
         __threadfence();
-        mbar_arrive(bar_epi_sync(hd));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_epi_sync(hd));
         ok = mbar_wait(bar_epi_sync(hd), epi_syncs & 1, wc, kWaitGroup);
         ++epi_syncs;
         if (!ok) break;
@@ -513,8 +516,8 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
   // ================================ teardown ==========================================
   if (ctl[0] != 0) {
     // a wait gave up: give in-flight bulk copies time to land before the CTA retires
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 400000ll) __nanosleep(1000);
   }
   tc_fence_before();
   __syncthreads();
