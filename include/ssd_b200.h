@@ -195,6 +195,35 @@ SSD_API int ssd_fused_state_fwd(const ssd_fused_state_params_t* prm, ssd_stream_
 SSD_API int ssd_check_status(void* workspace, ssd_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * 4b. ssd_fused_state_fwd without a caller-supplied workspace.  It has no counterpart in
+ *    the reference (whose wrappers allocate with torch.empty / torch.zeros on every call,
+ *    kernels/fused_concurrent.py:270-298).
+ *
+ *    For callers that cannot allocate device memory at the time of the call -- a server
+ *    that hands out all of its device memory once at start-up, a plug-in running inside
+ *    another runtime's callback, a loop that must not block on the allocator -- and so
+ *    cannot provide `workspace`.  Arguments and results are those of ssd_fused_state_fwd;
+ *    `workspace` and `workspace_bytes` are ignored.  The scratch lives in a device array
+ *    that is part of the library image: ssd_static_scratch_bytes() = 16 MiB on EVERY GPU
+ *    that loads the library, held until the process exits.
+ *
+ *    Limits and rules:
+ *      - a problem whose scratch need (ssd_fused_state_workspace_bytes) exceeds 16 MiB is
+ *        rejected with SSD_ERR_WORKSPACE and a message; the tcgen05 route always fits, the
+ *        plain-kernel route fits while batch*nchunks*nheads*headdim*dstate*4 bytes stay
+ *        under about 6 MiB (or without limit when `states` is passed);
+ *      - the call allocates and frees nothing: it looks up the array's device address,
+ *        clears its 4 KiB header with cudaMemsetAsync on `stream`, and launches;
+ *      - the first call on each device looks the address up (cudaGetSymbolAddress) with
+ *        that device current; make that first call before any stream capture begins;
+ *      - every call on a device shares the one array: two calls whose kernels may overlap
+ *        on the GPU (different streams, no dependency between them) race on it.  Calls
+ *        ordered on one stream are safe.
+ * ---------------------------------------------------------------------------------- */
+SSD_API size_t ssd_static_scratch_bytes(void);
+SSD_API int ssd_fused_state_fwd_static(const ssd_fused_state_params_t* prm, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * 5. chunk bmm.  Replaces _bmm_chunk_fwd, kernels/ssd_bmm.py:89-134 (device code :31-87).
  *    out[b,c,g,i,j] = sum_k a[b, c*L+i, g, k] * b[b, c*L+j, g, k]
  * ---------------------------------------------------------------------------------- */

@@ -271,6 +271,45 @@ std::tuple<Tensor, Tensor> fused_state_fwd(const Tensor& B, const Tensor& x, con
   return {out, fin};
 }
 
+// ssd_fused_state_fwd_static: the caller brings `out` and `final_states`; nothing is
+// allocated here or in the library (the scratch is the library's own static device array).
+void fused_state_fwd_static(const Tensor& B, const Tensor& x, const Tensor& dt, const Tensor& dA_cumsum,
+                            Tensor out, Tensor fin, const OptTensor& initial_states, const OptTensor& states_in,
+                            bool clamp_decay, bool force_general) {
+  TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor (libssd_b200 has no CPU path)");
+  c10::cuda::CUDAGuard guard(x.device());
+  ssd_fused_state_params_t p{};
+  Tensor hold;
+  fill_state_inputs(p.in, B, x, dt, dA_cumsum, std::nullopt, hold);
+  check_cuda(out, x, "out");
+  check_cuda(fin, x, "final_states");
+  TORCH_CHECK(out.dim() == 5 && out.stride(4) == 1, "out must be (b, c, h, p, n) with a contiguous last dimension");
+  TORCH_CHECK(fin.dim() == 4 && fin.stride(3) == 1 && fin.scalar_type() == at::kFloat,
+              "final_states must be fp32 (b, h, p, n) with a contiguous last dimension");
+  if (initial_states.has_value()) {
+    check_cuda(*initial_states, x, "initial_states");
+    TORCH_CHECK(initial_states->stride(3) == 1, "initial_states must be contiguous in its last dimension");
+    p.initial_states = initial_states->data_ptr();
+    p.init_dtype = dtype_code(*initial_states, "initial_states");
+    copy_strides(p.init_stride, *initial_states, {0, 1, 2});
+  }
+  if (states_in.has_value()) {
+    check_cuda(*states_in, x, "states");
+    TORCH_CHECK(states_in->stride(4) == 1, "states must be contiguous in its last dimension");
+    p.states = states_in->data_ptr();
+    p.states_dtype = dtype_code(*states_in, "states");
+    copy_strides(p.states_stride, *states_in, {0, 1, 2, 3});
+  }
+  p.out = out.data_ptr();
+  p.out_dtype = dtype_code(out, "out");
+  copy_strides(p.out_stride, out, {0, 1, 2, 3});
+  p.final_states = fin.data_ptr<float>();
+  copy_strides(p.final_stride, fin, {0, 1, 2});
+  p.clamp_decay = clamp_decay ? 1 : 0;
+  p.force_general = force_general ? 1 : 0;
+  check_rc(ssd_fused_state_fwd_static(&p, current_stream(x)), "ssd_fused_state_fwd_static");
+}
+
 // Synchronises and reports whether the last fused call on this device hit a wait limit.
 void check_status(const Tensor& like) {
   c10::cuda::CUDAGuard guard(like.device());
@@ -408,6 +447,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out_dtype") = py::none(), py::arg("initial_states") = py::none(), py::arg("seq_idx") = py::none(),
         py::arg("states") = py::none(), py::arg("states_in_fp32") = true, py::arg("clamp_decay") = true,
         py::arg("force_general") = false);
+  m.def("fused_state_fwd_static", &fused_state_fwd_static, py::arg("B"), py::arg("x"), py::arg("dt"),
+        py::arg("dA_cumsum"), py::arg("out"), py::arg("final_states"), py::arg("initial_states") = py::none(),
+        py::arg("states") = py::none(), py::arg("clamp_decay") = true, py::arg("force_general") = false);
+  m.def("static_scratch_bytes", []() { return ssd_static_scratch_bytes(); });
   m.def("check_status", &check_status, py::arg("like"));
   m.def("bmm_chunk_fwd", &bmm_chunk_fwd, py::arg("a"), py::arg("b"), py::arg("chunk_size"),
         py::arg("seq_idx") = py::none(), py::arg("causal") = false, py::arg("output_dtype") = py::none());
