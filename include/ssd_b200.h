@@ -275,6 +275,39 @@ typedef struct {
 
 SSD_API int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t stream);
 
+/* ------------------------------------------------------------------------------------
+ * 7. sequence-parallel fix-up.  No counterpart in the reference (it is single-GPU,
+ *    kernels/fused_concurrent.py:289); the carry it builds on is the reference's
+ *    initial_states / final_states pair (kernels/ssd_state_passing.py:61-65,81).
+ *
+ *    A sequence is cut into `world` chunk-aligned slices, one per rank.  Every rank first
+ *    runs ssd_fused_state_fwd on its slice with a zero carry-in (rank 0: the caller's
+ *    initial_states), which yields out0 (its passed states), Z_r (its final state) and
+ *    logP_r[b,h] = sum over its chunks of dA_cumsum[b,h,c,L-1].  After all ranks' (Z, logP)
+ *    have been gathered into local memory (NCCL all-gather or any other transport), this
+ *    call adds the carried state:
+ *        S_in   = sum_{j<rank} exp(sum_{j<k<rank} logP_k) * Z_j
+ *        out[c] = out0[c] + exp(sum_{k<c, local} dA_last_k) * S_in      (skipped where the
+ *                 factor is exactly zero in fp32, which leaves out[c] bit-identical)
+ *        final  = Z_rank + exp(logP_rank) * S_in
+ *    Rank 0 has nothing to add and returns at once.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const float* Z_all;         /* (world, b, h, dim) fp32 contiguous: every rank's slice-final state */
+  const float* logP_all;      /* (world, b, h) fp32 contiguous */
+  const float* dA_chunk_last; /* (b, h, c) fp32: dA_cumsum[..., L-1] of the local slice */
+  void* out;                  /* (b, c, h, dim) of out_dtype, dim contiguous; updated in place */
+  float* final_states;        /* (b, h, dim) fp32, dim contiguous; written */
+  int32_t out_dtype;
+  int32_t world, rank;
+  int32_t batch, nheads, nchunks, dim;
+  int64_t dA_stride[3];       /* b, h, c */
+  int64_t out_stride[3];      /* b, c, h */
+  int64_t final_stride[2];    /* b, h */
+} ssd_seqpar_fixup_params_t;
+
+SSD_API int ssd_seqpar_fixup(const ssd_seqpar_fixup_params_t* prm, ssd_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

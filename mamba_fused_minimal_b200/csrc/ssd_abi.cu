@@ -203,6 +203,18 @@ int ssd_check_status(void* workspace, ssd_stream_t stream) {
   return SSD_ERR_TIMEOUT;
 }
 
+int ssd_seqpar_fixup(const ssd_seqpar_fixup_params_t* prm, ssd_stream_t stream) {
+  SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
+  const ssd_seqpar_fixup_params_t& p = *prm;
+  SSD_REQUIRE(p.Z_all && p.logP_all && p.dA_chunk_last && p.out && p.final_states, SSD_ERR_BAD_ARGUMENT,
+              "Z_all, logP_all, dA_chunk_last, out and final_states must not be NULL");
+  SSD_REQUIRE(valid_dtype(p.out_dtype), SSD_ERR_BAD_ARGUMENT, "bad out_dtype %d", p.out_dtype);
+  SSD_REQUIRE(p.world > 0 && p.rank >= 0 && p.rank < p.world, SSD_ERR_BAD_ARGUMENT, "rank %d outside world %d",
+              p.rank, p.world);
+  SSD_REQUIRE(p.batch > 0 && p.nheads > 0 && p.nchunks > 0 && p.dim > 0, SSD_ERR_BAD_ARGUMENT, "sizes must be positive");
+  return launch_seqpar_fixup(p, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int ssd_bmm_chunk_fwd(const ssd_bmm_chunk_params_t* prm, ssd_stream_t stream) {
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_bmm_chunk_params_t& p = *prm;

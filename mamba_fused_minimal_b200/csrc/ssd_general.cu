@@ -157,6 +157,51 @@ int launch_state_passing(const ssd_state_passing_params_t& p, cudaStream_t strea
 }
 
 // =====================================================================================
+// sequence-parallel fix-up
+// =====================================================================================
+// Thread = one state element of one (batch, head).  The carried state is a weighted sum of
+// the earlier ranks' slice-final states (weights: products of the slice decays in between);
+// it is added to the local passed states chunk by chunk for as long as the accumulated
+// decay has not underflowed to zero, and to the local final state.
+__global__ void __launch_bounds__(256)
+seqpar_fixup_kernel(ssd_seqpar_fixup_params_t p) {
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  if (d >= p.dim) return;
+  const int64_t bh = (int64_t)b * p.nheads + h;
+  const int64_t zstride = (int64_t)p.batch * p.nheads * p.dim;
+  const int64_t lstride = (int64_t)p.batch * p.nheads;
+  float s_in = 0.0f;
+  float logw = 0.0f;                      // sum of logP_k for j < k < rank, built from the back
+  for (int j = p.rank - 1; j >= 0; --j) {
+    s_in = fmaf(fast_exp(logw), p.Z_all[(int64_t)j * zstride + bh * p.dim + d], s_in);
+    logw += p.logP_all[(int64_t)j * lstride + bh];
+  }
+  const int64_t abase = (int64_t)b * p.dA_stride[0] + (int64_t)h * p.dA_stride[1];
+  const int64_t obase = (int64_t)b * p.out_stride[0] + (int64_t)h * p.out_stride[2] + d;
+  float cum = 0.0f;
+  for (int c = 0; c < p.nchunks; ++c) {
+    const float f = fast_exp(cum);
+    if (f != 0.0f) {
+      const int64_t o = obase + (int64_t)c * p.out_stride[1];
+      store_f(p.out, p.out_dtype, o, fmaf(f, s_in, load_f(p.out, p.out_dtype, o)));
+    }
+    cum += p.dA_chunk_last[abase + (int64_t)c * p.dA_stride[2]];
+  }
+  const int64_t fo = (int64_t)b * p.final_stride[0] + (int64_t)h * p.final_stride[1] + d;
+  p.final_states[fo] = fmaf(fast_exp(cum), s_in, p.Z_all[(int64_t)p.rank * zstride + bh * p.dim + d]);
+}
+
+int launch_seqpar_fixup(const ssd_seqpar_fixup_params_t& p, cudaStream_t stream) {
+  SSD_REQUIRE(p.nheads <= 65535 && p.batch <= 65535, SSD_ERR_UNSUPPORTED, "fix-up grid too large");
+  dim3 grid((p.dim + 255) / 256, p.nheads, p.batch);
+  seqpar_fixup_kernel<<<grid, 256, 0, stream>>>(p);
+  SSD_CUDA_OK(cudaGetLastError());
+  return SSD_OK;
+}
+
+// =====================================================================================
 // tiled contraction template
 // =====================================================================================
 constexpr int TG_BM = 64, TG_BN = 64, TG_BK = 16, TG_THREADS = 256;

@@ -13,6 +13,7 @@ int launch_state_passing(const ssd_state_passing_params_t& p, cudaStream_t strea
 int launch_chunk_state_general(const ssd_chunk_state_params_t& p, int clamp_decay, cudaStream_t stream);
 int launch_bmm_chunk_general(const ssd_bmm_chunk_params_t& p, cudaStream_t stream);
 int launch_chunk_scan_general(const ssd_chunk_scan_params_t& p, cudaStream_t stream);
+int launch_seqpar_fixup(const ssd_seqpar_fixup_params_t& p, cudaStream_t stream);
 
 // ---- tcgen05 fused state kernel (ssd_fused_sm100.cu) ----------------------------------
 // Layout of the caller-supplied workspace used by the fused kernel.

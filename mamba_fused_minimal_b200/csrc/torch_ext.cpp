@@ -310,6 +310,46 @@ void fused_state_fwd_static(const Tensor& B, const Tensor& x, const Tensor& dt, 
   check_rc(ssd_fused_state_fwd_static(&p, current_stream(x)), "ssd_fused_state_fwd_static");
 }
 
+// Adds the state carried in from the earlier sequence slices (ssd_seqpar_fixup).  `out` and
+// `final_states` are updated in place.
+void seqpar_fixup(const Tensor& Z_all, const Tensor& logP_all, int64_t rank, const Tensor& dA_chunk_last, Tensor out,
+                  Tensor final_states) {
+  TORCH_CHECK(out.is_cuda(), "out must be a CUDA tensor (libssd_b200 has no CPU path)");
+  check_cuda(Z_all, out, "Z_all");
+  check_cuda(logP_all, out, "logP_all");
+  check_cuda(dA_chunk_last, out, "dA_chunk_last");
+  check_cuda(final_states, out, "final_states");
+  TORCH_CHECK(Z_all.is_contiguous() && logP_all.is_contiguous(), "gathered Z and logP must be contiguous");
+  TORCH_CHECK(Z_all.scalar_type() == at::kFloat && logP_all.scalar_type() == at::kFloat &&
+                  dA_chunk_last.scalar_type() == at::kFloat && final_states.scalar_type() == at::kFloat,
+              "Z, logP, dA_chunk_last and final_states must be fp32");
+  TORCH_CHECK(out.dim() == 5 && out.stride(4) == 1 && out.stride(3) == out.size(4), "out must be (b, c, h, p, n) with dense (p, n)");
+  TORCH_CHECK(final_states.dim() == 4 && final_states.stride(3) == 1 && final_states.stride(2) == final_states.size(3),
+              "final_states must be (b, h, p, n) with dense (p, n)");
+  c10::cuda::CUDAGuard guard(out.device());
+  ssd_seqpar_fixup_params_t p{};
+  p.Z_all = Z_all.data_ptr<float>();
+  p.logP_all = logP_all.data_ptr<float>();
+  p.dA_chunk_last = dA_chunk_last.data_ptr<float>();
+  p.out = out.data_ptr();
+  p.final_states = final_states.data_ptr<float>();
+  p.out_dtype = dtype_code(out, "out");
+  p.world = Z_all.size(0);
+  p.rank = rank;
+  p.batch = out.size(0);
+  p.nchunks = out.size(1);
+  p.nheads = out.size(2);
+  p.dim = out.size(3) * out.size(4);
+  TORCH_CHECK(Z_all.numel() == (int64_t)p.world * p.batch * p.nheads * p.dim, "Z_all has the wrong size");
+  TORCH_CHECK(logP_all.numel() == (int64_t)p.world * p.batch * p.nheads, "logP_all has the wrong size");
+  TORCH_CHECK(dA_chunk_last.dim() == 3 && dA_chunk_last.size(0) == p.batch && dA_chunk_last.size(1) == p.nheads &&
+                  dA_chunk_last.size(2) == p.nchunks, "dA_chunk_last must be (b, h, c)");
+  copy_strides(p.dA_stride, dA_chunk_last, {0, 1, 2});
+  copy_strides(p.out_stride, out, {0, 1, 2});
+  copy_strides(p.final_stride, final_states, {0, 1});
+  check_rc(ssd_seqpar_fixup(&p, current_stream(out)), "ssd_seqpar_fixup");
+}
+
 // Synchronises and reports whether the last fused call on this device hit a wait limit.
 void check_status(const Tensor& like) {
   c10::cuda::CUDAGuard guard(like.device());
@@ -451,6 +491,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("dA_cumsum"), py::arg("out"), py::arg("final_states"), py::arg("initial_states") = py::none(),
         py::arg("states") = py::none(), py::arg("clamp_decay") = true, py::arg("force_general") = false);
   m.def("static_scratch_bytes", []() { return ssd_static_scratch_bytes(); });
+  m.def("seqpar_fixup", &seqpar_fixup, py::arg("Z_all"), py::arg("logP_all"), py::arg("rank"),
+        py::arg("dA_chunk_last"), py::arg("out"), py::arg("final_states"));
   m.def("check_status", &check_status, py::arg("like"));
   m.def("bmm_chunk_fwd", &bmm_chunk_fwd, py::arg("a"), py::arg("b"), py::arg("chunk_size"),
         py::arg("seq_idx") = py::none(), py::arg("causal") = false, py::arg("output_dtype") = py::none());

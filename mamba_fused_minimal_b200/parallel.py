@@ -1,0 +1,93 @@
+"""Multi-GPU partitioning of the SSD state path.  One process per GPU (torch.distributed).
+
+Heads and batch shard with no communication: every kernel is independent per (batch, head)
+given its group's B, so a rank simply calls the single-GPU functions on its shard
+(`shard_heads`, `shard_batch` say which).
+
+A long sequence shards along the sequence.  The recurrence over chunks is affine in the
+carried state, S -> P * S + Z, so each rank scans its slice with a zero carry-in, the ranks
+exchange their slice summaries (Z: the slice-final state, log P: the slice's summed
+log-decay; 2.6 MB per rank at 80 heads), and a fix-up pass adds the carried state to the local
+passed states (`seqpar_fused_state_fwd`).  The exchange is one all-gather over NCCL; the
+gathered buffer is local memory, from which the fix-up kernel forms its own carry-in.
+
+The reference is single-GPU (device hard-coded, kernels/fused_concurrent.py:289); what makes
+sharding possible there is the initial_states / final_states pair
+(kernels/ssd_state_passing.py:61-65,81), which this module composes across ranks.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n, world, rank):
+    """Contiguous, near-equal split of range(n): (start, stop) of `rank`."""
+    base, rem = divmod(n, world)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+def shard_heads(nheads, ngroups, world, rank):
+    """Head range of `rank` and the matching group range.  Heads of one B/C group stay on one
+    GPU whenever there are at least `world` groups; with fewer groups (e.g. one) the heads are
+    split and every rank keeps the whole group tensor."""
+    ratio = nheads // ngroups
+    if ngroups >= world:
+        g0, g1 = shard_range(ngroups, world, rank)
+        return (g0 * ratio, g1 * ratio), (g0, g1)
+    h0, h1 = shard_range(nheads, world, rank)
+    return (h0, h1), (h0 // ratio, (h1 - 1) // ratio + 1)
+
+
+def shard_batch(batch, world, rank):
+    return shard_range(batch, world, rank)
+
+
+def shard_sequence(seqlen, chunk_size, world, rank):
+    """Chunk-aligned slice [start, stop) of the sequence for `rank` (whole chunks per rank, the
+    ragged last chunk on the last rank that has any)."""
+    nchunks = (seqlen + chunk_size - 1) // chunk_size
+    c0, c1 = shard_range(nchunks, world, rank)
+    return min(c0 * chunk_size, seqlen), min(c1 * chunk_size, seqlen)
+
+
+def exchange_carries(Z, logP, group=None):
+    """All-gather every rank's slice summary.  Z (b, h, p, n) fp32, logP (b, h) fp32.
+    Returns (Z_all (world, b, h, p, n), logP_all (world, b, h)), both local and contiguous."""
+    world = dist.get_world_size(group)
+    Z = Z.contiguous()
+    logP = logP.contiguous()
+    # gathered along dimension 0 (the form every backend accepts), then viewed as (world, ...)
+    Z_cat = torch.empty((world * Z.shape[0],) + tuple(Z.shape[1:]), dtype=Z.dtype, device=Z.device)
+    logP_cat = torch.empty((world * logP.shape[0],) + tuple(logP.shape[1:]), dtype=logP.dtype, device=logP.device)
+    dist.all_gather_into_tensor(Z_cat, Z, group=group)
+    dist.all_gather_into_tensor(logP_cat, logP, group=group)
+    return Z_cat.view((world,) + tuple(Z.shape)), logP_cat.view((world,) + tuple(logP.shape))
+
+
+def carry_in_state(Z_all, logP_all, rank):
+    """The state entering `rank`'s slice: sum_{j<rank} exp(sum_{j<k<rank} logP_k) * Z_j.
+    Plain torch, any device; the CUDA fix-up kernel computes the same thing internally."""
+    s_in = torch.zeros_like(Z_all[0])
+    logw = torch.zeros_like(logP_all[0])
+    for j in range(rank - 1, -1, -1):
+        s_in = s_in + torch.exp(logw)[..., None, None] * Z_all[j]
+        logw = logw + logP_all[j]
+    return s_in
+
+
+def seqpar_fused_state_fwd(B, x, dt, dA_cumsum, out_dtype, initial_states=None, group=None):
+    """Sequence-parallel form of the fused entry point.  Arguments are this rank's slice
+    (dt, dA_cumsum from `_chunk_cumsum_fwd` on the slice); `initial_states` is honoured on rank
+    0 only.  Returns (out, final) for the slice; `final` of the LAST rank is the sequence's
+    final state, and every rank's `final` is the state leaving its slice."""
+    from ._ext import C
+    from .kernels.fused_concurrent import _fused_chunk_state_state_passing_fwd_concurrent as fused
+    rank = dist.get_rank(group)
+    init = initial_states if rank == 0 else None
+    out, Z = fused(B, x, dt, dA_cumsum, out_dtype, initial_states=init)
+    dA_last = dA_cumsum[:, :, :, -1]
+    logP = dA_last.sum(dim=-1)
+    Z_all, logP_all = exchange_carries(Z, logP, group)
+    if rank > 0:
+        C.seqpar_fixup(Z_all, logP_all, rank, dA_last, out, Z)
+    return out, Z
