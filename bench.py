@@ -41,6 +41,9 @@ sys.path.insert(0, ROOT)
 WORKLOAD = dict(name="mamba2-2.7b-layer", batch=8, seqlen=4096, nheads=80, headdim=64, ngroups=1, dstate=128,
                 chunk_size=256)
 FALLBACK_HBM_GBS = 6650.0
+# DRAM traffic of the fused kernel per token, from the ncu capture summarised in
+# profiles/fused_state_kernel_mamba2-2.7b_batch4.md: (183.0 MB + 94.4 MB) / 16384 tokens
+NCU_TRAFFIC_PER_TOKEN = (183.02e6 + 94.4e6) / 16384
 
 
 def algorithmic_bytes(w, in_bytes=2, out_bytes=2, with_cumsum=True):
@@ -315,7 +318,11 @@ def main():
                            l2="inputs (365 MB read per step) exceed the 126 MB L2; no explicit flush",
                            path_bytes_per_step=algorithmic_bytes(w, with_cumsum=True)),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_PER_TOKEN * tokens_per_rank,
+                         "traffic_source": "ncu dram__bytes_read+write of a batch-4 capture (183.0 MB read; writes "
+                                           "counted as the 94.4 MB the launch must write, 64.9 MB of it reached DRAM "
+                                           "before the kernel ended), scaled by tokens",
+                         "peak_kind": peak_kind,
                          "kernel": "fused_state_kernel", "bytes_per_launch": fused_bytes,
                          "ms_per_launch": fused_mean_ms, "ms_per_launch_median": statistics.median(fused_ms),
                          "frac_of_8TBs": achieved / 8000.0,

@@ -243,6 +243,9 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld_32xN(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_32x32(taddr, r); }
+__device__ __forceinline__ void tmem_ld_32xN(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x16(taddr, r); }
+
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
 //   bits  0-13  start address >> 4          bits 16-29  leading-dimension byte offset >> 4
 //   bits 32-45  stride byte offset >> 4     bits 46-47  version (1)

@@ -19,10 +19,16 @@
 // Warp roles (HPC = heads per CTA sharing one B tile):
 //   warps [0, 4*HPC)      epilogue: one warpgroup per head; tcgen05.ld the chunk state,
 //                         S <- exp(dA_last) * S + state in registers, store out / final
-//   warp  4*HPC           TMA producer (x, B tiles; dt / dA_cumsum rows)
+//   warp  4*HPC           TMA producer: per 64-position stage the raw B tile and one x tile per
+//                         head; per chunk the dt / dA_cumsum rows (bulk copy)
 //   warp  4*HPC + 1       MMA issuer (one thread), TMEM allocation
 //   remaining warps       scale B by the per-position decay*dt in fp32, round to the input
-//                         type, write the MMA's A operand (generic -> async proxy fence)
+//                         type: the last head's A operand overwrites the raw tile in place,
+//                         the other heads' go to the stage's spare tiles (a thread reads its
+//                         16-byte pieces into registers before it writes any), then
+//                         generic -> async proxy fence and one mbarrier arrival per warp.
+// One ring of stages carries a tile through TMA -> scaling -> MMA, so the latency of each
+// handoff is covered by the ring depth instead of needing a second ring of scaled tiles.
 #include <cuda.h>
 
 #include <mutex>
@@ -48,24 +54,32 @@ enum WaitCode {
 
 template <int HPC>
 struct Cfg {
-  static constexpr int NS = (HPC == 1) ? 5 : 4;       // TMA stages
-  static constexpr int NT = (HPC == 1) ? 3 : 2;       // scaled-B slots (one tile per head each)
+  static constexpr int NS = (HPC == 1) ? 6 : 4;       // pipeline stages (TMA -> scale in place -> MMA)
+  static constexpr int NT = NS;                       // one 'scaled' barrier per stage
   static constexpr int ND = 2;                        // dt/dA row slots
   static constexpr int NBUF = 4;                      // TMEM accumulators per head
   static constexpr int EPI_WARPS = 4 * HPC;
-  static constexpr int SCALE_WARPS = (HPC == 1) ? 6 : 6;
+#ifndef SSD_SCALE_WARPS
+#define SSD_SCALE_WARPS 6
+#endif
+  static constexpr int SCALE_WARPS = SSD_SCALE_WARPS;
+  static constexpr int EPI_COLS = (EPI_WARPS + 2 + SCALE_WARPS) * 32 > 512 ? 16 : 32;
   static constexpr int WARPS = EPI_WARPS + 2 + SCALE_WARPS;
   static constexpr int THREADS = WARPS * 32;
   static constexpr int SCALE_THREADS = SCALE_WARPS * 32;
   static constexpr int RAWB_BYTES = kKT * kN * 2;     // 16 KiB: two 64-column SW128 boxes
   static constexpr int X_BYTES = kKT * kP * 2;        // 8 KiB: one SW128 box
-  static constexpr int STAGE_BYTES = RAWB_BYTES + HPC * X_BYTES;
+  // a stage: the raw B tile (scaled IN PLACE into the last head's A operand), one more A tile
+  // per further head, then one x tile per head
+  static constexpr int LOAD_BYTES = RAWB_BYTES + HPC * X_BYTES;   // what TMA brings per stage
+  static constexpr int OFF_XT = HPC * RAWB_BYTES;                 // x tiles inside a stage
+  static constexpr int STAGE_BYTES = HPC * RAWB_BYTES + HPC * X_BYTES;
   static constexpr int TMEM_COLS = HPC * NBUF * kP;   // 256 or 512
   // shared-memory map (byte offsets from a 1024-aligned base)
   static constexpr int OFF_STAGES = 0;
-  static constexpr int OFF_BS = OFF_STAGES + NS * STAGE_BYTES;
-  static constexpr int BS_SLOT = HPC * RAWB_BYTES;
-  static constexpr int OFF_DTDA = OFF_BS + NT * BS_SLOT;
+  static constexpr int OFF_DTDA = OFF_STAGES + NS * STAGE_BYTES;
+  // A-operand tile of head hd inside a stage: the last head reuses the raw tile's place
+  __host__ __device__ static constexpr int a_tile_off(int hd) { return hd == HPC - 1 ? 0 : (1 + hd) * RAWB_BYTES; }
   static constexpr int DTDA_SLOT = HPC * 2 * kMaxL * 4;
   static constexpr int OFF_SCALE = OFF_DTDA + ND * DTDA_SLOT;
   static constexpr int SCALE_SLOT = HPC * kMaxL * 4;
@@ -157,22 +171,25 @@ __device__ __forceinline__ uint32_t pack16(int dtype, float lo, float hi) {
   return dtype == SSD_BF16 ? Pack<__nv_bfloat16>::pack(lo, hi) : Pack<__half>::pack(lo, hi);
 }
 
-// Store 32 values v[i] = element (p0 + i, n) of a (kP x kN) row-major matrix whose rows
+// Store R values v[i] = element (p0 + i, n) of a (kP x kN) row-major matrix whose rows
 // start at `row0` (element pointer to (p0, 0)), row pitch `pitch` elements.  Thread `n`.
 // fp32: one coalesced 128-byte row segment per warp instruction.  16-bit: neighbouring
 // lanes swap one value so that each lane stores one packed pair (n, n+1) of one row.
-__device__ __forceinline__ void store_rows32(void* base, int dtype, int64_t elem_off, int64_t pitch,
-                                             int n, const float (&v)[32]) {
-  if (dtype == SSD_F32) {
+// WIDTH: 0 = decided at run time from `dtype`, 32 / 16 = known at compile time (keeps only one
+// of the two unrolled bodies in the instruction stream of the hot loop).
+template <int R, int WIDTH = 0>
+__device__ __forceinline__ void store_rows(void* base, int dtype, int64_t elem_off, int64_t pitch,
+                                           int n, const float (&v)[R]) {
+  if (WIDTH == 32 || (WIDTH == 0 && dtype == SSD_F32)) {
     float* o = static_cast<float*>(base) + elem_off + n;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) o[(int64_t)i * pitch] = v[i];
+    for (int i = 0; i < R; ++i) o[(int64_t)i * pitch] = v[i];
   } else {
     const bool odd = n & 1;
     uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(base) + elem_off +
                                               (odd ? pitch + n - 1 : n));
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
+    for (int i = 0; i < R; i += 2) {
       // even lane keeps row i and sends its row i+1 value; odd lane the other way round
       const float send = odd ? v[i] : v[i + 1];
       const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
@@ -182,7 +199,8 @@ __device__ __forceinline__ void store_rows32(void* base, int dtype, int64_t elem
   }
 }
 
-template <typename T, int HPC>
+
+template <typename T, int HPC, bool OUT32>
 __global__ void __launch_bounds__(Cfg<HPC>::THREADS, 1)
 fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
                    const __grid_constant__ CUtensorMap tmap_B, const FusedArgs a) {
@@ -200,7 +218,6 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
   auto bar_full = [&](int s) { return bars + 8u * s; };
   auto bar_empty = [&](int s) { return bars + 8u * (C::NS + s); };
   auto bar_bs_full = [&](int t) { return bars + 8u * (2 * C::NS + t); };
-  auto bar_bs_empty = [&](int t) { return bars + 8u * (2 * C::NS + C::NT + t); };
   auto bar_dd_full = [&](int r) { return bars + 8u * (2 * C::NS + 2 * C::NT + r); };
   auto bar_dd_empty = [&](int r) { return bars + 8u * (2 * C::NS + 2 * C::NT + C::ND + r); };
   auto bar_acc_full = [&](int b) { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + b); };
@@ -217,7 +234,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   if (tid == 0) {
     for (int s = 0; s < C::NS; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-    for (int t = 0; t < C::NT; ++t) { mbar_init(bar_bs_full(t), C::SCALE_WARPS); mbar_init(bar_bs_empty(t), 1); }
+    for (int t = 0; t < C::NT; ++t) mbar_init(bar_bs_full(t), C::SCALE_WARPS);
     for (int r = 0; r < C::ND; ++r) { mbar_init(bar_dd_full(r), 1); mbar_init(bar_dd_empty(r), 1); }
     for (int b = 0; b < C::NBUF; ++b) {
       mbar_init(bar_acc_full(b), 1);
@@ -281,14 +298,14 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
             const int s = it % C::NS;
             ok = mbar_wait(bar_empty(s), ((it / C::NS) & 1) ^ 1, wc, kWaitStageEmpty);
             if (!ok) break;
-            mbar_expect_tx(bar_full(s), C::STAGE_BYTES);
+            mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
             const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
             const int l0 = c * L + ks * kKT;
             tma_load_4d(st, &tmap_B, bar_full(s), 0, g, l0, b);
             tma_load_4d(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b);
 #pragma unroll
             for (int hd = 0; hd < HPC; ++hd)
-              tma_load_4d(st + C::RAWB_BYTES + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b);
+              tma_load_4d(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b);
           }
         }
       }
@@ -297,6 +314,11 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ============================== MMA issuer ========================================
     if (lane == 0) {
       constexpr uint32_t idesc = mma_idesc(Pack<T>::kFmt, true, true, kN, kP);
+      // Descriptors of slot 0 / stage 0, head 0; the address field (bits 0-13, units of
+      // 16 bytes) never carries out of its field for shared-memory addresses below 256 KiB,
+      // so other slots, heads and k-steps are reached by plain 64-bit additions.
+      const uint64_t adesc0 = smem_desc_sw128(sbase + C::OFF_STAGES, C::RAWB_BYTES / 2, 1024);
+      const uint64_t bdesc0 = smem_desc_sw128(sbase + C::OFF_STAGES + C::OFF_XT, C::X_BYTES, 1024);
       uint32_t it = 0, item = 0;
       bool ok = true;
       for (int j = 0; j < rg.m && ok; ++j) {
@@ -316,24 +338,21 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
             const int s = it % C::NS;
             ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
             if (!ok) break;
-            const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
-            const int t = it % C::NT;
-            ok = mbar_wait(bar_bs_full(t), (it / C::NT) & 1, wc, kWaitBsFull);
+            ok = mbar_wait(bar_bs_full(s), (it / C::NS) & 1, wc, kWaitBsFull);
             if (!ok) break;
             tc_fence_after();
+            const uint64_t ad_t = adesc0 + (uint64_t)((s * C::STAGE_BYTES) >> 4);
+            const uint64_t bd_s = bdesc0 + (uint64_t)((s * C::STAGE_BYTES) >> 4);
 #pragma unroll
             for (int hd = 0; hd < HPC; ++hd) {
-              const uint32_t a_base = sbase + C::OFF_BS + t * C::BS_SLOT + hd * C::RAWB_BYTES;
-              const uint32_t b_base = st + C::RAWB_BYTES + hd * C::X_BYTES;
               const uint32_t d_tmem = tmem_base + (hd * C::NBUF + buf) * kP;
 #pragma unroll
               for (int k16 = 0; k16 < kKT / 16; ++k16) {
-                const uint64_t ad = smem_desc_sw128(a_base + k16 * 2048, C::RAWB_BYTES / 2, 1024);
-                const uint64_t bd = smem_desc_sw128(b_base + k16 * 2048, C::X_BYTES, 1024);
+                const uint64_t ad = ad_t + (uint64_t)((C::a_tile_off(hd) + k16 * 2048) >> 4);
+                const uint64_t bd = bd_s + (uint64_t)((hd * C::X_BYTES + k16 * 2048) >> 4);
                 mma_f16_ss(d_tmem, ad, bd, idesc, (ks | k16) != 0 ? 1u : 0u);
               }
             }
-            mma_commit(bar_bs_empty(t));
             if (ok) mma_commit(bar_empty(s));
           }
           if (ok) mma_commit(bar_acc_full(buf));
@@ -354,12 +373,15 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (!ok) break;
         const float* dd = reinterpret_cast<const float*>(smem + C::OFF_DTDA + r * C::DTDA_SLOT);
         float* sc = reinterpret_cast<float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
-        for (int i = stid; i < HPC * L; i += C::SCALE_THREADS) {
-          const int hd = i / L, k = i - hd * L;
+#pragma unroll
+        for (int hd = 0; hd < HPC; ++hd) {
           const float* row = dd + hd * 2 * kMaxL;
-          float d = row[kMaxL + L - 1] - row[kMaxL + k];
-          if (a.clamp_decay) d = fminf(d, 0.0f);
-          sc[hd * kMaxL + k] = fast_exp(d) * row[k];
+          const float last = row[kMaxL + L - 1];
+          for (int k = stid; k < L; k += C::SCALE_THREADS) {
+            float d = last - row[kMaxL + k];
+            if (a.clamp_decay) d = fminf(d, 0.0f);
+            sc[hd * kMaxL + k] = fast_exp(d) * row[k];
+          }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_sc_sync());
@@ -373,26 +395,24 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
           ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
           if (!ok) break;
           const uint8_t* raw = smem + C::OFF_STAGES + s * C::STAGE_BYTES;
-          const int t = it % C::NT;
-          ok = mbar_wait(bar_bs_empty(t), ((it / C::NT) & 1) ^ 1, wc, kWaitBsEmpty);
-          if (!ok) break;
-          uint8_t* dst = smem + C::OFF_BS + t * C::BS_SLOT;
+          uint8_t* dst = smem + C::OFF_STAGES + s * C::STAGE_BYTES;
           const float* sch = sc + ks * kKT;
           // One pass over the raw B tile produces the scaled tile of every head of the CTA.
           // All loads of a thread are issued before the first use, so the shared-memory
           // latency is paid once per stage rather than once per 16 bytes.
           constexpr int kChunks = C::RAWB_BYTES / 16;
           constexpr int kPerThread = (kChunks + C::SCALE_THREADS - 1) / C::SCALE_THREADS;
+          const int vt = stid;
           uint4 v[kPerThread];
 #pragma unroll
           for (int q = 0; q < kPerThread; ++q) {
-            const int i = stid + q * C::SCALE_THREADS;
+            const int i = vt + q * C::SCALE_THREADS;
             if (kChunks % C::SCALE_THREADS == 0 || i < kChunks)
               v[q] = *reinterpret_cast<const uint4*>(raw + i * 16);
           }
 #pragma unroll
           for (int q = 0; q < kPerThread; ++q) {
-            const int i = stid + q * C::SCALE_THREADS;
+            const int i = vt + q * C::SCALE_THREADS;
             if (kChunks % C::SCALE_THREADS == 0 || i < kChunks) {
               const int off = i * 16;
               const int row = (off & (C::RAWB_BYTES / 2 - 1)) >> 7;      // k within the stage
@@ -412,13 +432,13 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 o.y = Pack<T>::pack(r1.x, r1.y);
                 o.z = Pack<T>::pack(r2.x, r2.y);
                 o.w = Pack<T>::pack(r3.x, r3.y);
-                *reinterpret_cast<uint4*>(dst + hd * C::RAWB_BYTES + off) = o;
+                *reinterpret_cast<uint4*>(dst + C::a_tile_off(hd) + off) = o;
               }
             }
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_bs_full(t));
+          if (lane == 0) mbar_arrive(bar_bs_full(s));
         }
       }
     }
@@ -427,6 +447,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int hd = warp >> 2;
     const int n = (warp & 3) * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    constexpr int kEW = C::EPI_COLS;      // accumulator columns handled per TMEM load
     float S[kP];
     uint32_t item = 0, epi_syncs = 0;
     bool ok = true;
@@ -464,32 +485,32 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
         tc_fence_after();
         const uint32_t taddr = tmem_base + lane_sel + (hd * C::NBUF + buf) * kP;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t raw[32];
-          tmem_ld_32x32(taddr + half * 32, raw);
+        for (int q = 0; q < kP / kEW; ++q) {
+          uint32_t raw[kEW];
+          tmem_ld_32xN(taddr + q * kEW, raw);
           tmem_ld_wait();
-          if (half == 1) {
+          if (q == kP / kEW - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_empty(hd, buf));
           }
-          float v[32];
+          float v[kEW];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+          for (int i = 0; i < kEW; ++i) v[i] = __uint_as_float(raw[i]);
           if (a.states != nullptr) {
             const int64_t so = (int64_t)b * a.states_s[0] + (int64_t)c * a.states_s[1] + (int64_t)h * a.states_s[2] +
-                               (int64_t)(half * 32) * a.states_s[3];
-            store_rows32(a.states, a.states_dtype, so, a.states_s[3], n, v);
+                               (int64_t)(q * kEW) * a.states_s[3];
+            store_rows<kEW>(a.states, a.states_dtype, so, a.states_s[3], n, v);
           }
           if (a.mode == 0) {
-            float cur[32];
+            float cur[kEW];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) cur[i] = S[half * 32 + i];
+            for (int i = 0; i < kEW; ++i) cur[i] = S[q * kEW + i];
             const int64_t oo = (int64_t)b * a.out_s[0] + (int64_t)c * a.out_s[1] + (int64_t)h * a.out_s[2] +
-                               (int64_t)(half * 32) * a.out_s[3];
-            store_rows32(a.out, a.out_dtype, oo, a.out_s[3], n, cur);
+                               (int64_t)(q * kEW) * a.out_s[3];
+            store_rows<kEW, OUT32 ? 32 : 16>(a.out, a.out_dtype, oo, a.out_s[3], n, cur);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) S[half * 32 + i] = fmaf(decay, cur[i], v[i]);
+            for (int i = 0; i < kEW; ++i) S[q * kEW + i] = fmaf(decay, cur[i], v[i]);
           }
         }
       }
@@ -644,7 +665,7 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
 
   const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
   const int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
-  auto kern = fused_state_kernel<T, HPC>;
+  auto kern = (p.out_dtype == SSD_F32 && mode == 0) ? fused_state_kernel<T, HPC, true> : fused_state_kernel<T, HPC, false>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(mx, mB, a);
   SSD_CUDA_OK(cudaGetLastError());
@@ -690,6 +711,7 @@ size_t fused_fast_workspace_bytes(const ssd_fused_state_params_t&) {
   return FusedWorkspaceLayout::kCarryOffset +
          (size_t)FusedWorkspaceLayout::kMaxCtas * 2 * kP * kN * sizeof(float);
 }
+
 
 int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream) {
   const int variant = fused_fast_variant(p, nullptr);
