@@ -175,6 +175,86 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+SEQ1M = dict(name="seq-1m", batch=1, seqlen=1048576, nheads=80, headdim=64, ngroups=1, dstate=128, chunk_size=256)
+
+
+def run_seq1m(args, rank, world, local):
+    """Long-context case: ONE 1 M-token sequence, sharded along the sequence over the ranks
+    (strong scaling).  A step = chunk cumsum of the slice + the sequence-parallel fused state
+    path (local scan from a zero carry, NCCL all-gather of slice summaries, fix-up)."""
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from mamba_fused_minimal_b200 import parallel as P
+    from mamba_fused_minimal_b200.kernels.fused_concurrent import _fused_chunk_state_state_passing_fwd_concurrent as fused
+    from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_state import _chunk_cumsum_fwd as cumsum
+    w = dict(SEQ1M)
+    if args.seqlen is not None:
+        w["seqlen"] = args.seqlen
+        w["name"] = f"seq-{args.seqlen}"
+    L = w["chunk_size"]
+    s0, s1 = P.shard_sequence(w["seqlen"], L, world, rank)
+    d = generate_benchmark_data(1, s1 - s0, w["nheads"], w["headdim"], w["ngroups"], w["dstate"],
+                                dtype=torch.bfloat16, device=dev, seed=rank)
+    x, B, dt, A, bias = d["x"], d["B"], d["dt"], d["A"], d["dt_bias"]
+
+    def step():
+        dA, dto = cumsum(dt, A, L, dt_bias=bias, dt_softplus=True)
+        if dist is None:
+            return fused(B, x, dto, dA, torch.bfloat16)
+        return P.seqpar_fused_state_fwd(B, x, dto, dA, torch.bfloat16)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
+    if sampler is not None:
+        sampler.start()
+    K = args.steps
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(K):
+        step()
+    end.record()
+    barrier()
+    total_ms = start.elapsed_time(end)
+    clocks = sampler.stop() if sampler is not None else None
+    from mamba_fused_minimal_b200._ext import C as _C
+    _C.check_status(x)
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = float(t.item()) / K
+        peak, peak_kind = measured_peak()
+        path_bytes = algorithmic_bytes(w, with_cumsum=True)
+        gbs = path_bytes / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "ssd_state_path_tokens_per_s", "value": w["seqlen"] / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload=w["name"], **{k: v for k, v in w.items() if k != "name"},
+                           parallelism=f"sequence sharded over {world} GPU(s); all-gather of slice summaries + fix-up",
+                           l2="inputs exceed the 126 MB L2; no explicit flush", path_bytes_per_step=path_bytes),
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak * world, "unit": "GB/s",
+                         "frac": gbs / (peak * world), "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "whole step (cumsum + fused + exchange + fix-up), all GPUs"},
+            "e2e": None, "gpu_launches": (2 if world == 1 else 3) * K, "clocks": clocks}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,6 +265,9 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="profiling aid: device-resident timing only")
     ap.add_argument("--batch", type=int, default=None,
                     help="profiling aid: override the workload's batch (the bench line then names it)")
+    ap.add_argument("--workload", default="mamba2-2.7b-layer", choices=["mamba2-2.7b-layer", "seq1m"],
+                    help="seq1m: the 1 M-token sequence-parallel case (extra; the default is the contract's workload)")
+    ap.add_argument("--seqlen", type=int, default=None, help="seq1m only: override the sequence length")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -197,6 +280,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    if args.workload == "seq1m":
+        run_seq1m(args, rank, world, local)
+        return
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist = None

@@ -108,6 +108,8 @@ struct FusedArgs {
   int init_dtype, out_dtype, states_dtype;
   int clamp_decay;
   int mode;               // 0: state passing fused; 1: per-chunk states only
+  int defer;              // non-zero: segments that start inside a strip start from zero; the
+                          // carried state is added afterwards by segment_fixup_kernel
 };
 
 struct Range {
@@ -466,6 +468,9 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
             for (int p = 0; p < kP; ++p) S[p] = 0.0f;
           }
+        } else if (a.defer) {
+#pragma unroll
+          for (int p = 0; p < kP; ++p) S[p] = 0.0f;
         } else {
           const int src = (int)blockIdx.x - 1;
           ok = flag_wait(a.flags + (size_t)src * HPC + hd, epoch_target, wc, kWaitCarry);
@@ -554,6 +559,110 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
       __threadfence();
       reinterpret_cast<volatile int*>(a.status)[1] = (int)epoch_target;
     }
+  }
+}
+
+// Second pass of the deferred-carry mode.  When strips are longer than a CTA's range, waiting
+// for the previous CTA's carry would serialise the CTAs of a strip, so every segment that
+// starts inside a strip is computed from a zero state and leaves its segment-final state in
+// its CTA's carry slot.  This kernel walks each (batch, head)'s segments in order, keeps the
+// state that was missing at each segment start, and adds it to that segment's passed states
+// (wherever the accumulated decay has not underflowed to zero) and to the final state.
+struct SegFixArgs {
+  const float* dA;          // dA_cumsum
+  const float* carry;       // [cta][HPC][kP * kN]
+  void* out;
+  float* final_states;
+  int64_t dA_s[3], out_s[4], final_s[3];
+  int out_dtype;
+  int batch, nheads, nchunks, chunk_size, hpc, strips_per_batch, grid;
+};
+
+// Block = one (batch, head); thread t owns state elements t, t + 256, ...  For each segment
+// warp 0 turns the chunk decays into per-chunk factors exp(sum of the earlier chunks' decays)
+// with a shuffle scan, 1024 chunks at a time, into shared memory; then every thread adds
+// factor * carry to its elements of the chunks whose factor is not zero.
+__global__ void __launch_bounds__(256) segment_fixup_kernel(const SegFixArgs a) {
+  constexpr int kTile = 1024;
+  constexpr int kPerThread = kP * kN / 256;
+  __shared__ float fac[kTile];
+  __shared__ float cum_carry;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int strip = b * a.strips_per_batch + h / a.hpc;
+  const int hd = h % a.hpc;
+  const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
+  const long long first = (long long)strip * a.nchunks;
+  const float* dA_last = a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (a.chunk_size - 1);
+  const int64_t obase = (int64_t)b * a.out_s[0] + (int64_t)h * a.out_s[2];
+  float carry[kPerThread];
+#pragma unroll
+  for (int e = 0; e < kPerThread; ++e) carry[e] = 0.0f;
+  bool have = false;
+  int c = 0;
+  while (c < a.nchunks) {
+    // the CTA of the fused kernel that owned item first + c, and where its range ends
+    const long long i = first + c;
+    const int k = (int)(((i + 1) * a.grid + total - 1) / total) - 1;
+    const long long hi = total * (long long)(k + 1) / a.grid;
+    const int seg_end = (int)min((long long)a.nchunks, hi - first);
+    float cum = 0.0f;                    // decay accumulated since the segment start (warp 0)
+    for (int t0 = c; t0 < seg_end; t0 += kTile) {
+      const int tn = min(kTile, seg_end - t0);
+      __syncthreads();
+      if (tid < 32) {
+        for (int j0 = 0; j0 < tn; j0 += 32) {
+          const int j = j0 + lane;
+          const float v = (j < tn) ? dA_last[(int64_t)(t0 + j) * a.dA_s[2]] : 0.0f;
+          float incl = v;
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += t;
+          }
+          if (j < tn) fac[j] = fast_exp(cum + incl - v);      // exclusive: decay of the earlier chunks
+          cum += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (tid == 0) cum_carry = cum;
+      }
+      __syncthreads();
+      if (have) {
+        for (int j = 0; j < tn; ++j) {
+          const float f = fac[j];
+          if (f != 0.0f) {
+            const int64_t ob = obase + (int64_t)(t0 + j) * a.out_s[1];
+#pragma unroll
+            for (int e = 0; e < kPerThread; ++e) {
+              const int d = tid + e * 256;
+              const int64_t o = ob + (d / kN) * a.out_s[3] + (d % kN);
+              store_f(a.out, a.out_dtype, o, fmaf(f, carry[e], load_f(a.out, a.out_dtype, o)));
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+    const float ftot = fast_exp(cum_carry);
+    if (seg_end == a.nchunks) {
+      if (have) {
+#pragma unroll
+        for (int e = 0; e < kPerThread; ++e) {
+          const int d = tid + e * 256;
+          float* fo = a.final_states + (int64_t)b * a.final_s[0] + (int64_t)h * a.final_s[1] +
+                      (d / kN) * a.final_s[2] + (d % kN);
+          *fo = fmaf(ftot, carry[e], *fo);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < kPerThread; ++e) {
+        const int d = tid + e * 256;
+        const float z = a.carry[((size_t)k * a.hpc + hd) * (kP * kN) + d];
+        carry[e] = have ? fmaf(ftot, carry[e], z) : z;
+      }
+      have = true;
+    }
+    c = seg_end;
   }
 }
 
@@ -664,11 +773,43 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   a.mode = mode;
 
   const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
-  const int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
+  const long long strips = (long long)a.batch * a.strips_per_batch;
+  int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
+  // Few, long strips (a long sequence with few heads): use a whole number of CTAs per strip.
+  // The ranges then start at the same chunk offsets in every strip, so at any moment the CTAs
+  // of different heads read the same B tiles (which otherwise would not survive in L2 between
+  // two heads' passes over a sequence whose B does not fit there).
+  if (mode == 0 && strips * 2 <= grid && a.nchunks >= 64) grid = (int)(strips * (grid / strips));
   auto kern = (p.out_dtype == SSD_F32 && mode == 0) ? fused_state_kernel<T, HPC, true> : fused_state_kernel<T, HPC, false>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  // A strip longer than a CTA's range would make the CTAs of that strip wait for one another
+  // in turn; then the carry is deferred to a second, small kernel instead.
+  // (Only when the ranges are long: for short ones the chained carry costs next to nothing and
+  // keeps the passed states free of the second rounding that a later correction implies.)
+  const long long per_cta = (total + grid - 1) / grid;
+  a.defer = (mode == 0 && a.nchunks > per_cta && per_cta >= 16) ? 1 : 0;
   kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(mx, mB, a);
   SSD_CUDA_OK(cudaGetLastError());
+  if (a.defer) {
+    SegFixArgs f{};
+    f.dA = a.dA;
+    f.carry = a.carry;
+    f.out = a.out;
+    f.final_states = a.final_states;
+    for (int i = 0; i < 3; ++i) { f.dA_s[i] = a.dA_s[i]; f.final_s[i] = a.final_s[i]; }
+    for (int i = 0; i < 4; ++i) f.out_s[i] = a.out_s[i];
+    f.out_dtype = a.out_dtype;
+    f.batch = a.batch;
+    f.nheads = a.nheads;
+    f.nchunks = a.nchunks;
+    f.chunk_size = a.chunk_size;
+    f.hpc = HPC;
+    f.strips_per_batch = a.strips_per_batch;
+    f.grid = grid;
+    SSD_REQUIRE(a.nheads <= 65535 && a.batch <= 65535, SSD_ERR_UNSUPPORTED, "fix-up grid too large");
+    segment_fixup_kernel<<<dim3(a.nheads, a.batch), 256, 0, stream>>>(f);
+    SSD_CUDA_OK(cudaGetLastError());
+  }
   return SSD_OK;
 }
 
