@@ -578,13 +578,17 @@ struct SegFixArgs {
   int batch, nheads, nchunks, chunk_size, hpc, strips_per_batch, grid;
 };
 
-// Block = one (batch, head); thread t owns state elements t, t + 256, ...  For each segment
+// Block = one (batch, head) and one of kSegFixSplit slices of the state; thread t owns elements
+// t, t + 256, ... of the slice.  For each segment
 // warp 0 turns the chunk decays into per-chunk factors exp(sum of the earlier chunks' decays)
 // with a shuffle scan, 1024 chunks at a time, into shared memory; then every thread adds
 // factor * carry to its elements of the chunks whose factor is not zero.
+constexpr int kSegFixSplit = 8;
+
 __global__ void __launch_bounds__(256) segment_fixup_kernel(const SegFixArgs a) {
   constexpr int kTile = 1024;
-  constexpr int kPerThread = kP * kN / 256;
+  constexpr int kPerThread = kP * kN / 256 / kSegFixSplit;
+  const int dbase = blockIdx.z * (kP * kN / kSegFixSplit);
   __shared__ float fac[kTile];
   __shared__ float cum_carry;
   const int tid = threadIdx.x, lane = tid & 31;
@@ -633,7 +637,7 @@ __global__ void __launch_bounds__(256) segment_fixup_kernel(const SegFixArgs a) 
             const int64_t ob = obase + (int64_t)(t0 + j) * a.out_s[1];
 #pragma unroll
             for (int e = 0; e < kPerThread; ++e) {
-              const int d = tid + e * 256;
+              const int d = dbase + tid + e * 256;
               const int64_t o = ob + (d / kN) * a.out_s[3] + (d % kN);
               store_f(a.out, a.out_dtype, o, fmaf(f, carry[e], load_f(a.out, a.out_dtype, o)));
             }
@@ -647,7 +651,7 @@ __global__ void __launch_bounds__(256) segment_fixup_kernel(const SegFixArgs a) 
       if (have) {
 #pragma unroll
         for (int e = 0; e < kPerThread; ++e) {
-          const int d = tid + e * 256;
+          const int d = dbase + tid + e * 256;
           float* fo = a.final_states + (int64_t)b * a.final_s[0] + (int64_t)h * a.final_s[1] +
                       (d / kN) * a.final_s[2] + (d % kN);
           *fo = fmaf(ftot, carry[e], *fo);
@@ -656,7 +660,7 @@ __global__ void __launch_bounds__(256) segment_fixup_kernel(const SegFixArgs a) 
     } else {
 #pragma unroll
       for (int e = 0; e < kPerThread; ++e) {
-        const int d = tid + e * 256;
+        const int d = dbase + tid + e * 256;
         const float z = a.carry[((size_t)k * a.hpc + hd) * (kP * kN) + d];
         carry[e] = have ? fmaf(ftot, carry[e], z) : z;
       }
@@ -807,7 +811,7 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
     f.strips_per_batch = a.strips_per_batch;
     f.grid = grid;
     SSD_REQUIRE(a.nheads <= 65535 && a.batch <= 65535, SSD_ERR_UNSUPPORTED, "fix-up grid too large");
-    segment_fixup_kernel<<<dim3(a.nheads, a.batch), 256, 0, stream>>>(f);
+    segment_fixup_kernel<<<dim3(a.nheads, a.batch, kSegFixSplit), 256, 0, stream>>>(f);
     SSD_CUDA_OK(cudaGetLastError());
   }
   return SSD_OK;
