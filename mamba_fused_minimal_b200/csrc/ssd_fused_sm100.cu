@@ -782,8 +782,9 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   // Few, long strips (a long sequence with few heads): use a whole number of CTAs per strip.
   // The ranges then start at the same chunk offsets in every strip, so at any moment the CTAs
   // of different heads read the same B tiles (which otherwise would not survive in L2 between
-  // two heads' passes over a sequence whose B does not fit there).
-  if (mode == 0 && strips * 2 <= grid && a.nchunks >= 64) grid = (int)(strips * (grid / strips));
+  // two heads' passes over a sequence whose B does not fit there; when B fits, all SMs are used).
+  const long long B_bytes = (long long)a.batch * a.seqlen * a.ngroups * kN * 2;
+  if (mode == 0 && strips * 2 <= grid && B_bytes > (64ll << 20)) grid = (int)(strips * (grid / strips));
   auto kern = (p.out_dtype == SSD_F32 && mode == 0) ? fused_state_kernel<T, HPC, true> : fused_state_kernel<T, HPC, false>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   // A strip longer than a CTA's range would make the CTAs of that strip wait for one another
