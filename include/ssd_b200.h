@@ -287,14 +287,15 @@ SSD_API int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t 
  *    have been gathered into local memory (NCCL all-gather or any other transport), this
  *    call adds the carried state:
  *        S_in   = sum_{j<rank} exp(sum_{j<k<rank} logP_k) * Z_j
- *        out[c] = out0[c] + exp(sum_{k<c, local} dA_last_k) * S_in      (skipped where the
- *                 factor is exactly zero in fp32, which leaves out[c] bit-identical)
+ *        out[c] = out0[c] + exp(sum_{k<c, local} dA_last_k) * S_in      (skipped, leaving out[c]
+ *                 bit-identical, where the factor is zero in fp32; for a 16-bit out also where
+ *                 it is at most 2^-24, far below what that type resolves)
  *        final  = Z_rank + exp(logP_rank) * S_in
  *    Rank 0 has nothing to add and returns at once.
  * ---------------------------------------------------------------------------------- */
 typedef struct {
-  const float* Z_all;         /* (world, b, h, dim) fp32 contiguous: every rank's slice-final state */
-  const float* logP_all;      /* (world, b, h) fp32 contiguous */
+  const float* Z_all;         /* (world, b, h, dim) fp32, dense per rank: every rank's slice-final state */
+  const float* logP_all;      /* (world, b, h) fp32, dense per rank */
   const float* dA_chunk_last; /* (b, h, c) fp32: dA_cumsum[..., L-1] of the local slice */
   void* out;                  /* (b, c, h, dim) of out_dtype, dim contiguous; updated in place */
   float* final_states;        /* (b, h, dim) fp32, dim contiguous; written */
@@ -304,6 +305,8 @@ typedef struct {
   int64_t dA_stride[3];       /* b, h, c */
   int64_t out_stride[3];      /* b, c, h */
   int64_t final_stride[2];    /* b, h */
+  int64_t Z_rank_stride;      /* elements between two ranks' Z; 0 = b * h * dim (contiguous) */
+  int64_t logP_rank_stride;   /* elements between two ranks' logP; 0 = b * h (contiguous) */
 } ssd_seqpar_fixup_params_t;
 
 SSD_API int ssd_seqpar_fixup(const ssd_seqpar_fixup_params_t* prm, ssd_stream_t stream);

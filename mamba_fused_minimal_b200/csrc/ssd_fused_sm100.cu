@@ -34,6 +34,7 @@
 #include <mutex>
 
 #include "sm100_ptx.cuh"
+#include "ssd_carry.cuh"
 #include "ssd_common.cuh"
 #include "ssd_launch.h"
 
@@ -273,6 +274,9 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (warp == C::EPI_WARPS) {
     // ============================== TMA producer ======================================
     if (lane == 0) {
+      // B is read once per head of its group and should stay in L2 between those reads;
+      // x is read exactly once.
+      const uint64_t keep = l2_policy_evict_last(), stream_once = l2_policy_evict_first();
       uint32_t it = 0, item = 0;
       bool ok = true;
       for (int j = 0; j < rg.m && ok; ++j) {
@@ -303,11 +307,11 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
             mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
             const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
             const int l0 = c * L + ks * kKT;
-            tma_load_4d(st, &tmap_B, bar_full(s), 0, g, l0, b);
-            tma_load_4d(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b);
+            tma_load_4d_hint(st, &tmap_B, bar_full(s), 0, g, l0, b, keep);
+            tma_load_4d_hint(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b, keep);
 #pragma unroll
             for (int hd = 0; hd < HPC; ++hd)
-              tma_load_4d(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b);
+              tma_load_4d_hint(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b, stream_once);
           }
         }
       }
@@ -576,32 +580,31 @@ struct SegFixArgs {
   int64_t dA_s[3], out_s[4], final_s[3];
   int out_dtype;
   int batch, nheads, nchunks, chunk_size, hpc, strips_per_batch, grid;
+  int vec;                  // passed-state rows allow 8-byte (16-bit types) / 16-byte (fp32) accesses
 };
 
-// Block = one (batch, head) and one of kSegFixSplit slices of the state; thread t owns elements
-// t, t + 256, ... of the slice.  For each segment
-// warp 0 turns the chunk decays into per-chunk factors exp(sum of the earlier chunks' decays)
-// with a shuffle scan, 1024 chunks at a time, into shared memory; then every thread adds
-// factor * carry to its elements of the chunks whose factor is not zero.
-constexpr int kSegFixSplit = 8;
+// Block = one (batch, head) and one of kSegFixSplit slices of the state; a thread owns four
+// consecutive elements of the slice.  For each segment the block builds the per-chunk factors
+// exp(sum of the earlier chunks' decays), 1024 chunks at a time, and adds factor * carry to
+// its elements of the chunks whose factor is above the cut-off of the output type.
+constexpr int kSegFixSplit = kP * kN / (kCarryThreads * kCarryQuad);
 
-__global__ void __launch_bounds__(256) segment_fixup_kernel(const SegFixArgs a) {
-  constexpr int kTile = 1024;
-  constexpr int kPerThread = kP * kN / 256 / kSegFixSplit;
-  const int dbase = blockIdx.z * (kP * kN / kSegFixSplit);
-  __shared__ float fac[kTile];
-  __shared__ float cum_carry;
-  const int tid = threadIdx.x, lane = tid & 31;
+__global__ void __launch_bounds__(kCarryThreads) segment_fixup_kernel(const SegFixArgs a) {
+  __shared__ __align__(16) float fac[kCarryTile];
+  __shared__ float cum_slot;
+  const int tid = threadIdx.x;
+  const int d0 = blockIdx.z * (kCarryThreads * kCarryQuad) + tid * kCarryQuad;   // first owned element
   const int h = blockIdx.x, b = blockIdx.y;
   const int strip = b * a.strips_per_batch + h / a.hpc;
   const int hd = h % a.hpc;
   const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
   const long long first = (long long)strip * a.nchunks;
   const float* dA_last = a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (a.chunk_size - 1);
-  const int64_t obase = (int64_t)b * a.out_s[0] + (int64_t)h * a.out_s[2];
-  float carry[kPerThread];
+  const int64_t obase = (int64_t)b * a.out_s[0] + (int64_t)h * a.out_s[2] + (d0 / kN) * a.out_s[3] + (d0 % kN);
+  const float cut = carry_cutoff(a.out_dtype);
+  float carry[kCarryQuad];
 #pragma unroll
-  for (int e = 0; e < kPerThread; ++e) carry[e] = 0.0f;
+  for (int e = 0; e < kCarryQuad; ++e) carry[e] = 0.0f;
   bool have = false;
   int c = 0;
   while (c < a.nchunks) {
@@ -610,58 +613,26 @@ __global__ void __launch_bounds__(256) segment_fixup_kernel(const SegFixArgs a) 
     const int k = (int)(((i + 1) * a.grid + total - 1) / total) - 1;
     const long long hi = total * (long long)(k + 1) / a.grid;
     const int seg_end = (int)min((long long)a.nchunks, hi - first);
-    float cum = 0.0f;                    // decay accumulated since the segment start (warp 0)
-    for (int t0 = c; t0 < seg_end; t0 += kTile) {
-      const int tn = min(kTile, seg_end - t0);
-      __syncthreads();
-      if (tid < 32) {
-        for (int j0 = 0; j0 < tn; j0 += 32) {
-          const int j = j0 + lane;
-          const float v = (j < tn) ? dA_last[(int64_t)(t0 + j) * a.dA_s[2]] : 0.0f;
-          float incl = v;
-#pragma unroll
-          for (int off = 1; off < 32; off <<= 1) {
-            const float t = __shfl_up_sync(0xffffffffu, incl, off);
-            if (lane >= off) incl += t;
-          }
-          if (j < tn) fac[j] = fast_exp(cum + incl - v);      // exclusive: decay of the earlier chunks
-          cum += __shfl_sync(0xffffffffu, incl, 31);
-        }
-        if (tid == 0) cum_carry = cum;
-      }
-      __syncthreads();
-      if (have) {
-        for (int j = 0; j < tn; ++j) {
-          const float f = fac[j];
-          if (f != 0.0f) {
-            const int64_t ob = obase + (int64_t)(t0 + j) * a.out_s[1];
-#pragma unroll
-            for (int e = 0; e < kPerThread; ++e) {
-              const int d = dbase + tid + e * 256;
-              const int64_t o = ob + (d / kN) * a.out_s[3] + (d % kN);
-              store_f(a.out, a.out_dtype, o, fmaf(f, carry[e], load_f(a.out, a.out_dtype, o)));
-            }
-          }
-        }
-      }
+    float cum = 0.0f;                    // decay accumulated since the segment start
+    for (int t0 = c; t0 < seg_end; t0 += kCarryTile) {
+      const int tn = min(kCarryTile, seg_end - t0);
+      cum = chunk_factors(dA_last + (int64_t)t0 * a.dA_s[2], a.dA_s[2], tn, cum, fac, &cum_slot);
+      if (have)
+        add_carry_tile_any(a.out, a.out_dtype, a.vec != 0, obase + (int64_t)t0 * a.out_s[1], a.out_s[1], fac, tn, cut,
+                           carry, kCarryQuad);
     }
-    __syncthreads();
-    const float ftot = fast_exp(cum_carry);
+    const float ftot = fast_exp(cum);
     if (seg_end == a.nchunks) {
       if (have) {
+        float* fo = a.final_states + (int64_t)b * a.final_s[0] + (int64_t)h * a.final_s[1] +
+                    (d0 / kN) * a.final_s[2] + (d0 % kN);
 #pragma unroll
-        for (int e = 0; e < kPerThread; ++e) {
-          const int d = dbase + tid + e * 256;
-          float* fo = a.final_states + (int64_t)b * a.final_s[0] + (int64_t)h * a.final_s[1] +
-                      (d / kN) * a.final_s[2] + (d % kN);
-          *fo = fmaf(ftot, carry[e], *fo);
-        }
+        for (int e = 0; e < kCarryQuad; ++e) fo[e] = fmaf(ftot, carry[e], fo[e]);
       }
     } else {
 #pragma unroll
-      for (int e = 0; e < kPerThread; ++e) {
-        const int d = dbase + tid + e * 256;
-        const float z = a.carry[((size_t)k * a.hpc + hd) * (kP * kN) + d];
+      for (int e = 0; e < kCarryQuad; ++e) {
+        const float z = a.carry[((size_t)k * a.hpc + hd) * (kP * kN) + d0 + e];
         carry[e] = have ? fmaf(ftot, carry[e], z) : z;
       }
       have = true;
@@ -779,12 +750,6 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
   const long long strips = (long long)a.batch * a.strips_per_batch;
   int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
-  // Few, long strips (a long sequence with few heads): use a whole number of CTAs per strip.
-  // The ranges then start at the same chunk offsets in every strip, so at any moment the CTAs
-  // of different heads read the same B tiles (which otherwise would not survive in L2 between
-  // two heads' passes over a sequence whose B does not fit there; when B fits, all SMs are used).
-  const long long B_bytes = (long long)a.batch * a.seqlen * a.ngroups * kN * 2;
-  if (mode == 0 && strips * 2 <= grid && B_bytes > (64ll << 20)) grid = (int)(strips * (grid / strips));
   auto kern = (p.out_dtype == SSD_F32 && mode == 0) ? fused_state_kernel<T, HPC, true> : fused_state_kernel<T, HPC, false>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   // A strip longer than a CTA's range would make the CTAs of that strip wait for one another
@@ -811,6 +776,8 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
     f.hpc = HPC;
     f.strips_per_batch = a.strips_per_batch;
     f.grid = grid;
+    f.vec = reinterpret_cast<uintptr_t>(p.out) % (kCarryQuad * dtype_size(p.out_dtype)) == 0;
+    for (int i = 0; i < 4; ++i) f.vec = f.vec && a.out_s[i] % kCarryQuad == 0;
     SSD_REQUIRE(a.nheads <= 65535 && a.batch <= 65535, SSD_ERR_UNSUPPORTED, "fix-up grid too large");
     segment_fixup_kernel<<<dim3(a.nheads, a.batch, kSegFixSplit), 256, 0, stream>>>(f);
     SSD_CUDA_OK(cudaGetLastError());

@@ -6,6 +6,7 @@
 // One tiled-GEMM kernel template serves the three contractions (per-chunk state, C.B^T,
 // chunk scan); each is a "problem" struct that says how to fetch an operand element, what
 // to do between the two accumulation phases and how to store a result element.
+#include "ssd_carry.cuh"
 #include "ssd_common.cuh"
 #include "ssd_launch.h"
 
@@ -159,88 +160,61 @@ int launch_state_passing(const ssd_state_passing_params_t& p, cudaStream_t strea
 // =====================================================================================
 // sequence-parallel fix-up
 // =====================================================================================
-// Block = one (batch, head) and one slice of up to 2048 state elements; a thread owns up to 8
-// of them.  The carried state is a weighted sum of the earlier ranks' slice-final states
-// (weights: products of the slice decays in between).  Warp 0 turns the local chunk decays
-// into per-chunk factors exp(sum of the earlier chunks' decays) with a shuffle scan, 1024
-// chunks at a time; every thread then adds factor * carried state to its elements of the
-// chunks whose factor has not underflowed to zero, and to the local final state.
-constexpr int SP_SLICE = 2048;
-constexpr int SP_PER_THREAD = SP_SLICE / 256;
+// Block = one (batch, head) and one slice of 1024 state elements; a thread owns four
+// consecutive ones.  The carried state is a weighted sum of the earlier ranks' slice-final
+// states (weights: products of the slice decays in between).  The block turns the local chunk
+// decays into per-chunk factors exp(sum of the earlier chunks' decays), 1024 chunks at a
+// time, and adds factor * carried state to its elements of the chunks whose factor is above
+// the cut-off of the output type, and to the local final state.
+constexpr int SP_SLICE = kCarryThreads * kCarryQuad;
 
-__global__ void __launch_bounds__(256)
-seqpar_fixup_kernel(ssd_seqpar_fixup_params_t p) {
-  constexpr int kTile = 1024;
-  __shared__ float fac[kTile];
-  __shared__ float cum_total;
-  const int tid = threadIdx.x, lane = tid & 31;
+__global__ void __launch_bounds__(kCarryThreads)
+seqpar_fixup_kernel(ssd_seqpar_fixup_params_t p, int vec) {
+  __shared__ __align__(16) float fac[kCarryTile];
+  __shared__ float cum_slot;
+  const int tid = threadIdx.x;
   const int h = blockIdx.x, b = blockIdx.y;
-  const int dbase = blockIdx.z * SP_SLICE;
+  const int d0 = blockIdx.z * SP_SLICE + tid * kCarryQuad;
+  const int n = max(0, min(kCarryQuad, p.dim - d0));          // owned elements that exist
   const int64_t bh = (int64_t)b * p.nheads + h;
-  const int64_t zstride = (int64_t)p.batch * p.nheads * p.dim;
-  const int64_t lstride = (int64_t)p.batch * p.nheads;
-  float s_in[SP_PER_THREAD];
+  const int64_t zstride = p.Z_rank_stride != 0 ? p.Z_rank_stride : (int64_t)p.batch * p.nheads * p.dim;
+  const int64_t lstride = p.logP_rank_stride != 0 ? p.logP_rank_stride : (int64_t)p.batch * p.nheads;
+  float s_in[kCarryQuad];
 #pragma unroll
-  for (int e = 0; e < SP_PER_THREAD; ++e) s_in[e] = 0.0f;
+  for (int e = 0; e < kCarryQuad; ++e) s_in[e] = 0.0f;
   float logw = 0.0f;                      // sum of logP_k for j < k < rank, built from the back
   for (int j = p.rank - 1; j >= 0; --j) {
     const float w = fast_exp(logw);
 #pragma unroll
-    for (int e = 0; e < SP_PER_THREAD; ++e) {
-      const int d = dbase + tid + e * 256;
-      if (d < p.dim) s_in[e] = fmaf(w, p.Z_all[(int64_t)j * zstride + bh * p.dim + d], s_in[e]);
-    }
+    for (int e = 0; e < kCarryQuad; ++e)
+      if (e < n) s_in[e] = fmaf(w, p.Z_all[(int64_t)j * zstride + bh * p.dim + d0 + e], s_in[e]);
     logw += p.logP_all[(int64_t)j * lstride + bh];
   }
-  const int64_t abase = (int64_t)b * p.dA_stride[0] + (int64_t)h * p.dA_stride[1];
-  const int64_t obase = (int64_t)b * p.out_stride[0] + (int64_t)h * p.out_stride[2];
-  float cum = 0.0f;                       // warp 0: decay accumulated since the slice start
-  for (int t0 = 0; t0 < p.nchunks; t0 += kTile) {
-    const int tn = min(kTile, p.nchunks - t0);
-    __syncthreads();
-    if (tid < 32) {
-      for (int j0 = 0; j0 < tn; j0 += 32) {
-        const int j = j0 + lane;
-        const float v = (j < tn) ? p.dA_chunk_last[abase + (int64_t)(t0 + j) * p.dA_stride[2]] : 0.0f;
-        float incl = v;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-          const float t = __shfl_up_sync(0xffffffffu, incl, off);
-          if (lane >= off) incl += t;
-        }
-        if (j < tn) fac[j] = fast_exp(cum + incl - v);
-        cum += __shfl_sync(0xffffffffu, incl, 31);
-      }
-      if (tid == 0) cum_total = cum;
-    }
-    __syncthreads();
-    for (int j = 0; j < tn; ++j) {
-      const float f = fac[j];
-      if (f != 0.0f) {
-        const int64_t ob = obase + (int64_t)(t0 + j) * p.out_stride[1];
-#pragma unroll
-        for (int e = 0; e < SP_PER_THREAD; ++e) {
-          const int d = dbase + tid + e * 256;
-          if (d < p.dim) store_f(p.out, p.out_dtype, ob + d, fmaf(f, s_in[e], load_f(p.out, p.out_dtype, ob + d)));
-        }
-      }
-    }
+  const float* decay = p.dA_chunk_last + (int64_t)b * p.dA_stride[0] + (int64_t)h * p.dA_stride[1];
+  const int64_t obase = (int64_t)b * p.out_stride[0] + (int64_t)h * p.out_stride[2] + d0;
+  const float cut = carry_cutoff(p.out_dtype);
+  float cum = 0.0f;                       // decay accumulated since the slice start
+  for (int t0 = 0; t0 < p.nchunks; t0 += kCarryTile) {
+    const int tn = min(kCarryTile, p.nchunks - t0);
+    cum = chunk_factors(decay + (int64_t)t0 * p.dA_stride[2], p.dA_stride[2], tn, cum, fac, &cum_slot);
+    if (n > 0)
+      add_carry_tile_any(p.out, p.out_dtype, vec != 0 && n == kCarryQuad, obase + (int64_t)t0 * p.out_stride[1],
+                         p.out_stride[1], fac, tn, cut, s_in, n);
   }
-  __syncthreads();
-  const float ftot = fast_exp(cum_total);
+  const float ftot = fast_exp(cum);
   const int64_t fo = (int64_t)b * p.final_stride[0] + (int64_t)h * p.final_stride[1];
 #pragma unroll
-  for (int e = 0; e < SP_PER_THREAD; ++e) {
-    const int d = dbase + tid + e * 256;
-    if (d < p.dim)
-      p.final_states[fo + d] = fmaf(ftot, s_in[e], p.Z_all[(int64_t)p.rank * zstride + bh * p.dim + d]);
-  }
+  for (int e = 0; e < kCarryQuad; ++e)
+    if (e < n)
+      p.final_states[fo + d0 + e] = fmaf(ftot, s_in[e], p.Z_all[(int64_t)p.rank * zstride + bh * p.dim + d0 + e]);
 }
 
 int launch_seqpar_fixup(const ssd_seqpar_fixup_params_t& p, cudaStream_t stream) {
   SSD_REQUIRE(p.nheads <= 65535 * 32 && p.batch <= 65535, SSD_ERR_UNSUPPORTED, "fix-up grid too large");
   dim3 grid(p.nheads, p.batch, (p.dim + SP_SLICE - 1) / SP_SLICE);
-  seqpar_fixup_kernel<<<grid, 256, 0, stream>>>(p);
+  bool vec = reinterpret_cast<uintptr_t>(p.out) % (kCarryQuad * dtype_size(p.out_dtype)) == 0;
+  for (int i = 0; i < 3; ++i) vec = vec && p.out_stride[i] % kCarryQuad == 0;
+  seqpar_fixup_kernel<<<grid, kCarryThreads, 0, stream>>>(p, vec ? 1 : 0);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }

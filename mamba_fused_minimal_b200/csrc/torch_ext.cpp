@@ -226,7 +226,7 @@ std::tuple<Tensor, Tensor> fused_state_fwd(const Tensor& B, const Tensor& x, con
                                            const Tensor& dA_cumsum, std::optional<at::ScalarType> out_dtype,
                                            const OptTensor& initial_states, const OptTensor& seq_idx,
                                            const OptTensor& states_in, bool states_in_fp32, bool clamp_decay,
-                                           bool force_general) {
+                                           bool force_general, const OptTensor& final_out) {
   TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor (libssd_b200 has no CPU path)");
   c10::cuda::CUDAGuard guard(x.device());
   ssd_fused_state_params_t p{};
@@ -241,7 +241,17 @@ std::tuple<Tensor, Tensor> fused_state_fwd(const Tensor& B, const Tensor& x, con
                                                          : (states_in_fp32 ? at::kFloat : B.scalar_type());
   const at::ScalarType odt = out_dtype.value_or(states_dt);
   Tensor out = torch::empty({batch, nchunks, nheads, headdim, dstate}, torch::dtype(odt).device(x.device()));
-  Tensor fin = torch::empty({batch, nheads, headdim, dstate}, torch::dtype(at::kFloat).device(x.device()));
+  // final_out: a caller-owned place for the final states (e.g. a slot of an exchange buffer)
+  Tensor fin;
+  if (final_out.has_value()) {
+    fin = *final_out;
+    check_cuda(fin, x, "final_states");
+    TORCH_CHECK(fin.scalar_type() == at::kFloat && fin.dim() == 4 && fin.size(0) == batch && fin.size(1) == nheads &&
+                    fin.size(2) == headdim && fin.size(3) == dstate && fin.stride(3) == 1,
+                "final_states must be fp32 (b, h, p, n) with a contiguous last dimension");
+  } else {
+    fin = torch::empty({batch, nheads, headdim, dstate}, torch::dtype(at::kFloat).device(x.device()));
+  }
   if (initial_states.has_value()) {
     check_cuda(*initial_states, x, "initial_states");
     TORCH_CHECK(initial_states->stride(3) == 1, "initial_states must be contiguous in its last dimension");
@@ -319,7 +329,8 @@ void seqpar_fixup(const Tensor& Z_all, const Tensor& logP_all, int64_t rank, con
   check_cuda(logP_all, out, "logP_all");
   check_cuda(dA_chunk_last, out, "dA_chunk_last");
   check_cuda(final_states, out, "final_states");
-  TORCH_CHECK(Z_all.is_contiguous() && logP_all.is_contiguous(), "gathered Z and logP must be contiguous");
+  TORCH_CHECK(Z_all.dim() == 5 && logP_all.dim() == 3 && Z_all[0].is_contiguous() && logP_all[0].is_contiguous(),
+              "gathered Z (world, b, h, p, n) and logP (world, b, h) must be dense per rank");
   TORCH_CHECK(Z_all.scalar_type() == at::kFloat && logP_all.scalar_type() == at::kFloat &&
                   dA_chunk_last.scalar_type() == at::kFloat && final_states.scalar_type() == at::kFloat,
               "Z, logP, dA_chunk_last and final_states must be fp32");
@@ -335,6 +346,8 @@ void seqpar_fixup(const Tensor& Z_all, const Tensor& logP_all, int64_t rank, con
   p.final_states = final_states.data_ptr<float>();
   p.out_dtype = dtype_code(out, "out");
   p.world = Z_all.size(0);
+  p.Z_rank_stride = Z_all.stride(0);
+  p.logP_rank_stride = logP_all.stride(0);
   p.rank = rank;
   p.batch = out.size(0);
   p.nchunks = out.size(1);
@@ -486,7 +499,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fused_state_fwd", &fused_state_fwd, py::arg("B"), py::arg("x"), py::arg("dt"), py::arg("dA_cumsum"),
         py::arg("out_dtype") = py::none(), py::arg("initial_states") = py::none(), py::arg("seq_idx") = py::none(),
         py::arg("states") = py::none(), py::arg("states_in_fp32") = true, py::arg("clamp_decay") = true,
-        py::arg("force_general") = false);
+        py::arg("force_general") = false, py::arg("final_states") = py::none());
   m.def("fused_state_fwd_static", &fused_state_fwd_static, py::arg("B"), py::arg("x"), py::arg("dt"),
         py::arg("dA_cumsum"), py::arg("out"), py::arg("final_states"), py::arg("initial_states") = py::none(),
         py::arg("states") = py::none(), py::arg("clamp_decay") = true, py::arg("force_general") = false);

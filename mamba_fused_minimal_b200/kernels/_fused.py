@@ -4,7 +4,7 @@ from .._ext import C as _C
 
 def _fused_chunk_state_state_passing_fwd(B, x, dt, dA_cumsum, out_dtype, initial_states=None, seq_idx=None,
                                          states=None, states_in_fp32=True, clamp_decay=True,
-                                         force_general=False):
+                                         force_general=False, final_states=None):
     batch, seqlen, nheads, headdim = x.shape
     _, _, nchunks, chunk_size = dt.shape
     _, _, ngroups, dstate = B.shape
@@ -19,4 +19,4 @@ def _fused_chunk_state_state_passing_fwd(B, x, dt, dA_cumsum, out_dtype, initial
     if initial_states is not None:
         assert initial_states.shape == (batch, nheads, headdim, dstate)
     return _C.fused_state_fwd(B, x, dt, dA_cumsum, out_dtype, initial_states, seq_idx, states,
-                              bool(states_in_fp32), bool(clamp_decay), bool(force_general))
+                              bool(states_in_fp32), bool(clamp_decay), bool(force_general), final_states)

@@ -50,18 +50,37 @@ def shard_sequence(seqlen, chunk_size, world, rank):
     return min(c0 * chunk_size, seqlen), min(c1 * chunk_size, seqlen)
 
 
-def exchange_carries(Z, logP, group=None):
-    """All-gather every rank's slice summary.  Z (b, h, p, n) fp32, logP (b, h) fp32.
-    Returns (Z_all (world, b, h, p, n), logP_all (world, b, h)), both local and contiguous."""
+def summary_buffer(batch, nheads, headdim, dstate, device):
+    """One rank's slice summary as a single fp32 buffer, so that one collective moves it:
+    returns (buf, Z, logP) where Z (b, h, p, n) and logP (b, h) are views into buf."""
+    nz = batch * nheads * headdim * dstate
+    buf = torch.empty(nz + batch * nheads, dtype=torch.float32, device=device)
+    return buf, buf[:nz].view(batch, nheads, headdim, dstate), buf[nz:].view(batch, nheads)
+
+
+def exchange_summaries(buf, shape, group=None):
+    """All-gather the ranks' summary buffers (from `summary_buffer`, shape = (b, h, p, n)).
+    Returns (Z_all (world, b, h, p, n), logP_all (world, b, h)): views into the one gathered,
+    local buffer."""
     world = dist.get_world_size(group)
-    Z = Z.contiguous()
-    logP = logP.contiguous()
-    # gathered along dimension 0 (the form every backend accepts), then viewed as (world, ...)
-    Z_cat = torch.empty((world * Z.shape[0],) + tuple(Z.shape[1:]), dtype=Z.dtype, device=Z.device)
-    logP_cat = torch.empty((world * logP.shape[0],) + tuple(logP.shape[1:]), dtype=logP.dtype, device=logP.device)
-    dist.all_gather_into_tensor(Z_cat, Z, group=group)
-    dist.all_gather_into_tensor(logP_cat, logP, group=group)
-    return Z_cat.view((world,) + tuple(Z.shape)), logP_cat.view((world,) + tuple(logP.shape))
+    b, h, p, n = shape
+    nz = b * h * p * n
+    gathered = torch.empty(world * buf.numel(), dtype=buf.dtype, device=buf.device)
+    dist.all_gather_into_tensor(gathered, buf, group=group)
+    g = gathered.view(world, buf.numel())
+    Z_all = g[:, :nz].unflatten(1, (b, h, p, n))
+    logP_all = g[:, nz:].unflatten(1, (b, h))
+    return Z_all, logP_all
+
+
+def exchange_carries(Z, logP, group=None):
+    """All-gather every rank's slice summary given as two tensors: Z (b, h, p, n) fp32,
+    logP (b, h) fp32.  Returns (Z_all (world, b, h, p, n), logP_all (world, b, h))."""
+    b, h, p, n = Z.shape
+    buf, Zv, lv = summary_buffer(b, h, p, n, Z.device)
+    Zv.copy_(Z)
+    lv.copy_(logP)
+    return exchange_summaries(buf, (b, h, p, n), group)
 
 
 def carry_in_state(Z_all, logP_all, rank):
@@ -81,13 +100,17 @@ def seqpar_fused_state_fwd(B, x, dt, dA_cumsum, out_dtype, initial_states=None, 
     0 only.  Returns (out, final) for the slice; `final` of the LAST rank is the sequence's
     final state, and every rank's `final` is the state leaving its slice."""
     from ._ext import C
-    from .kernels.fused_concurrent import _fused_chunk_state_state_passing_fwd_concurrent as fused
+    from .kernels._fused import _fused_chunk_state_state_passing_fwd as fused
     rank = dist.get_rank(group)
     init = initial_states if rank == 0 else None
-    out, Z = fused(B, x, dt, dA_cumsum, out_dtype, initial_states=init)
+    batch, _, nheads, headdim = x.shape
+    dstate = B.shape[-1]
+    # the local scan leaves its final state directly in the buffer that is exchanged
+    buf, Z, logP = summary_buffer(batch, nheads, headdim, dstate, x.device)
+    out, _ = fused(B, x, dt, dA_cumsum, out_dtype, initial_states=init, final_states=Z)
     dA_last = dA_cumsum[:, :, :, -1]
-    logP = dA_last.sum(dim=-1)
-    Z_all, logP_all = exchange_carries(Z, logP, group)
+    torch.sum(dA_last, dim=-1, out=logP)
+    Z_all, logP_all = exchange_summaries(buf, (batch, nheads, headdim, dstate), group)
     if rank > 0:
-        C.seqpar_fixup(Z_all, logP_all, rank, dA_last, out, Z)
+        C.seqpar_fixup(Z_all, logP_all, rank, dA_last, out, Z)      # Z becomes the state leaving the slice
     return out, Z
