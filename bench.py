@@ -250,7 +250,9 @@ def run_seq1m(args, rank, world, local):
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak * world, "unit": "GB/s",
                          "frac": gbs / (peak * world), "traffic": None, "peak_kind": peak_kind,
                          "kernel": "whole step (cumsum + fused + exchange + fix-up), all GPUs"},
-            "e2e": None, "gpu_launches": (2 if world == 1 else 3) * K, "clocks": clocks}), flush=True)
+            "e2e": None,
+            # per rank: cumsum, fused kernel, segment fix-up, and (ranks > 0) the cross-rank fix-up
+            "gpu_launches": (3 if world == 1 else 4) * K, "clocks": clocks}), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
