@@ -77,6 +77,9 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 // `code` in the global status word and returns false; every other waiter in the CTA sees
 // the flag and returns false too.  The limit is measured with the SM's own cycle counter,
 // which costs a few cycles to read, and only consulted once per 256 polls.
+// The wait loops are inlined: a kernel that re-balances registers between its roles
+// (setmaxnreg) cannot contain real calls, ptxas refuses to allocate registers for it.
+#define SSD_SLOWPATH __forceinline__
 constexpr long long kWaitLimitCycles = 4000000000ll;
 
 struct WaitCtx {
@@ -86,7 +89,7 @@ struct WaitCtx {
 
 // `sleep_ns` > 0 makes the waiter back off between polls: for roles that wait long and are
 // not on the critical path, so that their polling does not take issue slots from the rest.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx w, int code,
+__device__ SSD_SLOWPATH bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx w, int code,
                                             uint32_t sleep_ns) {
   long long t0 = 0;
   uint32_t it = 0;
@@ -120,7 +123,7 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __noinline__ bool flag_wait(const uint32_t* flag, uint32_t target, WaitCtx w, int code) {
+__device__ SSD_SLOWPATH bool flag_wait(const uint32_t* flag, uint32_t target, WaitCtx w, int code) {
   if (ld_acquire_gpu(flag) == target) return true;
   long long t0 = 0;
   uint32_t it = 0;
@@ -262,6 +265,49 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 
+// 16 lanes x 32 consecutive fp32 columns in the matrix-fragment arrangement: with g = thread / 4
+// and q = thread % 4, registers 4j+0 and 4j+1 receive (lane L0 + g, columns 8j + 2q and
+// 8j + 2q + 1), registers 4j+2 and 4j+3 the same columns of lane L0 + g + 8; L0 is the lane
+// field of the address (0 or 16 inside the warp's 32 lanes).
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// Four 8x8 matrices of 16-bit elements, stored transposed: register i of thread t holds
+// elements (row 2 * (t % 4), column t / 4) and (row 2 * (t % 4) + 1, column t / 4) of matrix
+// i, low half first; thread t supplies the address of row t % 8 of matrix t / 8 (16 bytes).
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t row_addr, uint32_t r0, uint32_t r1, uint32_t r2,
+                                                  uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};"
+               ::"r"(row_addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+// Untiled bulk copy shared -> global as part of the calling thread's current bulk group; both
+// addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+// Tiled store shared -> global through a 5-D tensor map, part of the thread's current bulk group.
+__device__ __forceinline__ void tma_store_5d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1, int c2,
+                                             int c3, int c4) {
+  asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+               ::"l"(map), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// All bulk groups of the calling thread have finished reading their shared-memory source.
+__device__ __forceinline__ void bulk_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// All bulk groups of the calling thread are complete.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_32xN(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_32x32(taddr, r); }
 __device__ __forceinline__ void tmem_ld_32xN(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x16(taddr, r); }
 

@@ -61,11 +61,14 @@ struct Cfg {
   static constexpr int NBUF = 4;                      // TMEM accumulators per head
   static constexpr int EPI_WARPS = 4 * HPC;
 #ifndef SSD_SCALE_WARPS
-#define SSD_SCALE_WARPS 6
+#define SSD_SCALE_WARPS 8
 #endif
   static constexpr int SCALE_WARPS = SSD_SCALE_WARPS;
-  static constexpr int EPI_COLS = (EPI_WARPS + 2 + SCALE_WARPS) * 32 > 512 ? 16 : 32;
-  static constexpr int WARPS = EPI_WARPS + 2 + SCALE_WARPS;
+  // one warpgroup of service warps: TMA producer, MMA issuer, two scale-vector warps
+  static constexpr int SERVICE_WARPS = 4;
+  static constexpr int SCV_THREADS = 64;
+  static constexpr int SCALE_WARP0 = EPI_WARPS + SERVICE_WARPS;
+  static constexpr int WARPS = SCALE_WARP0 + SCALE_WARPS;
   static constexpr int THREADS = WARPS * 32;
   static constexpr int SCALE_THREADS = SCALE_WARPS * 32;
   static constexpr int RAWB_BYTES = kKT * kN * 2;     // 16 KiB: two 64-column SW128 boxes
@@ -85,11 +88,30 @@ struct Cfg {
   static constexpr int OFF_SCALE = OFF_DTDA + ND * DTDA_SLOT;
   static constexpr int SCALE_SLOT = HPC * kMaxL * 4;
   static constexpr int OFF_BARS = OFF_SCALE + 2 * SCALE_SLOT;
-  static constexpr int NUM_BARS = 2 * NS + 2 * NT + 2 * ND + NBUF + HPC * NBUF + 1 + HPC;
+  static constexpr int NUM_BARS = 2 * NS + 2 * NT + 2 * ND + NBUF + HPC * NBUF + 4 + HPC;
   static constexpr int OFF_CTL = OFF_BARS + NUM_BARS * 8;
-  static constexpr int SMEM_BYTES = OFF_CTL + 64 + 1024;   // + alignment slack
+  // staging for 16-bit passed states: every epilogue warp owns 32 rows (p) x 32 columns (its
+  // dstate quadrant) = 32 x 64 bytes, laid out as a TMA box with the 64-byte swizzle
+  static constexpr int STAGING_BYTES = 32 * 64;
+  static constexpr int OFF_STAGING = (OFF_CTL + 64 + 1023) / 1024 * 1024;
+  static constexpr int SMEM_BYTES = OFF_STAGING + EPI_WARPS * STAGING_BYTES + 1024;   // + alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-  static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns must be a power of two");
+  // Register budget per role (setmaxnreg), used where the CTA has more than 512 threads and
+  // would otherwise be held to the launch allocation of LAUNCH_REGS per thread, too few for the
+  // epilogue's 64 state values.  setmaxnreg.inc waits for registers that other roles give back,
+  // so the per-role counts must fit in what the CTA is launched with, or the wait never ends.
+#ifndef SSD_REGS_EPI
+#define SSD_REGS_EPI 136
+#define SSD_REGS_SCALE 80
+#define SSD_REGS_SERVICE 40
+#endif
+  static constexpr bool REBALANCE = WARPS * 32 > 512;
+  static constexpr int LAUNCH_REGS = 65536 / (WARPS * 32) / 8 * 8;
+  static constexpr int REGS_EPI = SSD_REGS_EPI, REGS_SCALE = SSD_REGS_SCALE, REGS_SERVICE = SSD_REGS_SERVICE;
+  static_assert(!REBALANCE || (EPI_WARPS * REGS_EPI + SERVICE_WARPS * REGS_SERVICE + SCALE_WARPS * REGS_SCALE) <=
+                                  WARPS * LAUNCH_REGS, "per-role register counts exceed the launch allocation");
+  static_assert(!REBALANCE || (REGS_SCALE <= LAUNCH_REGS && REGS_SERVICE <= LAUNCH_REGS && REGS_EPI >= LAUNCH_REGS),
+                "scaling and service roles give registers back, the epilogue takes them");
 };
 
 struct FusedArgs {
@@ -112,6 +134,15 @@ struct FusedArgs {
   int defer;              // non-zero: segments that start inside a strip start from zero; the
                           // carried state is added afterwards by segment_fixup_kernel
 };
+
+#ifdef SSD_EXP_PROF
+__device__ long long g_prof[160 * 32];
+#define PROF_T() clock64()
+#define PROF_ADD(i, v) prof[(i)] += (v)
+#else
+#define PROF_T() 0ll
+#define PROF_ADD(i, v)
+#endif
 
 struct Range {
   long long lo, hi;
@@ -170,43 +201,10 @@ template <> struct Pack<__half> {
   }
 };
 
-__device__ __forceinline__ uint32_t pack16(int dtype, float lo, float hi) {
-  return dtype == SSD_BF16 ? Pack<__nv_bfloat16>::pack(lo, hi) : Pack<__half>::pack(lo, hi);
-}
-
-// Store R values v[i] = element (p0 + i, n) of a (kP x kN) row-major matrix whose rows
-// start at `row0` (element pointer to (p0, 0)), row pitch `pitch` elements.  Thread `n`.
-// fp32: one coalesced 128-byte row segment per warp instruction.  16-bit: neighbouring
-// lanes swap one value so that each lane stores one packed pair (n, n+1) of one row.
-// WIDTH: 0 = decided at run time from `dtype`, 32 / 16 = known at compile time (keeps only one
-// of the two unrolled bodies in the instruction stream of the hot loop).
-template <int R, int WIDTH = 0>
-__device__ __forceinline__ void store_rows(void* base, int dtype, int64_t elem_off, int64_t pitch,
-                                           int n, const float (&v)[R]) {
-  if (WIDTH == 32 || (WIDTH == 0 && dtype == SSD_F32)) {
-    float* o = static_cast<float*>(base) + elem_off + n;
-#pragma unroll
-    for (int i = 0; i < R; ++i) o[(int64_t)i * pitch] = v[i];
-  } else {
-    const bool odd = n & 1;
-    uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(base) + elem_off +
-                                              (odd ? pitch + n - 1 : n));
-#pragma unroll
-    for (int i = 0; i < R; i += 2) {
-      // even lane keeps row i and sends its row i+1 value; odd lane the other way round
-      const float send = odd ? v[i] : v[i + 1];
-      const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-      const uint32_t w = odd ? pack16(dtype, recv, v[i + 1]) : pack16(dtype, v[i], recv);
-      o[(int64_t)i * pitch / 2] = w;
-    }
-  }
-}
-
-
 template <typename T, int HPC, bool OUT32>
 __global__ void __launch_bounds__(Cfg<HPC>::THREADS, 1)
-fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                   const __grid_constant__ CUtensorMap tmap_B, const FusedArgs a) {
+fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_B,
+                   const __grid_constant__ CUtensorMap tmap_out, const FusedArgs a) {
   using C = Cfg<HPC>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -228,9 +226,12 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
     return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + hd * C::NBUF + b);
   };
   // group barriers (an mbarrier instead of bar.sync so that the wait is bounded like the rest)
-  auto bar_sc_sync = [&]() { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF); };
+  // scale-vector slots (two, alternating by item): filled by the scale-vector warps, read by
+  // the B-scaling warps
+  auto bar_sc_ready = [&](int i) { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF + i); };
+  auto bar_sc_free = [&](int i) { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF + 2 + i); };
   auto bar_epi_sync = [&](int hd) {
-    return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF + 1 + hd);
+    return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF + 4 + hd);
   };
   volatile int* ctl = reinterpret_cast<volatile int*>(smem + C::OFF_CTL);   // [0] abort, [1] tmem, [2] epoch
   WaitCtx wc{ctl, a.status};
@@ -238,13 +239,13 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (tid == 0) {
     for (int s = 0; s < C::NS; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
     for (int t = 0; t < C::NT; ++t) mbar_init(bar_bs_full(t), C::SCALE_WARPS);
-    for (int r = 0; r < C::ND; ++r) { mbar_init(bar_dd_full(r), 1); mbar_init(bar_dd_empty(r), 1); }
+    for (int r = 0; r < C::ND; ++r) { mbar_init(bar_dd_full(r), 1); mbar_init(bar_dd_empty(r), C::SCV_THREADS / 32); }
     for (int b = 0; b < C::NBUF; ++b) {
       mbar_init(bar_acc_full(b), 1);
       for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_acc_empty(hd, b), 4);
     }
     // group barriers take ONE arrival per warp: arrivals on one mbarrier serialise
-    mbar_init(bar_sc_sync(), C::SCALE_WARPS);
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_sc_ready(i), C::SCV_THREADS / 32); mbar_init(bar_sc_free(i), C::SCALE_WARPS); }
     for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_epi_sync(hd), 4);
     ctl[0] = 0;
     ctl[2] = reinterpret_cast<volatile int*>(a.status)[1];     // epoch of the previous launch
@@ -258,6 +259,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (warp == C::EPI_WARPS && lane == 0) {
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_B);
+    if (!OUT32 && a.mode == 0) prefetch_tensormap(&tmap_out);
   }
   tc_fence_before();
   __syncthreads();
@@ -271,6 +273,8 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const Range rg = make_range(total, nchunks);
   const int ratio = a.nheads / a.ngroups;
 
+  if (warp >= C::EPI_WARPS && warp < C::SCALE_WARP0) {
+  if constexpr (C::REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REGS_SERVICE));
   if (warp == C::EPI_WARPS) {
     // ============================== TMA producer ======================================
     if (lane == 0) {
@@ -279,6 +283,11 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint64_t keep = l2_policy_evict_last(), stream_once = l2_policy_evict_first();
       uint32_t it = 0, item = 0;
       bool ok = true;
+#ifdef SSD_EXP_PROF
+      long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      volatile long long* t_issue = reinterpret_cast<volatile long long*>(smem + C::OFF_CTL + 16);
+      const long long tstart = clock64();
+#endif
       for (int j = 0; j < rg.m && ok; ++j) {
         int strip, c0, c1;
         get_segment(rg, nchunks, j, strip, c0, c1);
@@ -287,8 +296,11 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int g = h0 / ratio;
         for (int c = c0; c < c1 && ok; ++c, ++item) {
           const int r = item % C::ND;
+          long long tp0 = PROF_T();
           ok = mbar_wait(bar_dd_empty(r), ((item / C::ND) & 1) ^ 1, wc, kWaitDdEmpty);
           if (!ok) break;
+          long long tp1 = PROF_T();
+          PROF_ADD(0, tp1 - tp0);
           mbar_expect_tx(bar_dd_full(r), HPC * 2 * L * 4);
 #pragma unroll
           for (int hd = 0; hd < HPC; ++hd) {
@@ -300,10 +312,17 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
           const int limit = min(L, a.seqlen - c * L);
           const int ksteps = (limit + kKT - 1) / kKT;
+          PROF_ADD(1, PROF_T() - tp1);
           for (int ks = 0; ks < ksteps; ++ks, ++it) {
             const int s = it % C::NS;
+            long long tq0 = PROF_T();
             ok = mbar_wait(bar_empty(s), ((it / C::NS) & 1) ^ 1, wc, kWaitStageEmpty);
             if (!ok) break;
+            long long tq1 = PROF_T();
+            PROF_ADD(2, tq1 - tq0);
+#ifdef SSD_EXP_PROF
+            t_issue[s] = tq1;
+#endif
             mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
             const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
             const int l0 = c * L + ks * kKT;
@@ -312,9 +331,14 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
             for (int hd = 0; hd < HPC; ++hd)
               tma_load_4d_hint(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b, stream_once);
+            PROF_ADD(3, PROF_T() - tq1);
           }
         }
       }
+#ifdef SSD_EXP_PROF
+      prof[7] = clock64() - tstart;
+      for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + i] = prof[i];
+#endif
     }
   } else if (warp == C::EPI_WARPS + 1) {
     // ============================== MMA issuer ========================================
@@ -327,25 +351,43 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint64_t bdesc0 = smem_desc_sw128(sbase + C::OFF_STAGES + C::OFF_XT, C::X_BYTES, 1024);
       uint32_t it = 0, item = 0;
       bool ok = true;
+#ifdef SSD_EXP_PROF
+      long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      volatile long long* t_issue = reinterpret_cast<volatile long long*>(smem + C::OFF_CTL + 16);
+      const long long tstart = clock64();
+#endif
       for (int j = 0; j < rg.m && ok; ++j) {
         int strip, c0, c1;
         get_segment(rg, nchunks, j, strip, c0, c1);
         for (int c = c0; c < c1 && ok; ++c, ++item) {
           const int buf = item % C::NBUF;
+          long long tm0 = PROF_T();
 #pragma unroll
           for (int hd = 0; hd < HPC; ++hd) {
             if (ok) ok = mbar_wait(bar_acc_empty(hd, buf), ((item / C::NBUF) & 1) ^ 1, wc, kWaitAccEmpty);
           }
           if (!ok) break;
+          PROF_ADD(0, PROF_T() - tm0);
           tc_fence_after();
           const int limit = min(L, a.seqlen - c * L);
           const int ksteps = (limit + kKT - 1) / kKT;
           for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
             const int s = it % C::NS;
+            long long tn0 = PROF_T();
+#ifdef SSD_EXP_PROF
+            const bool had_to_wait = !mbar_test_wait(bar_full(s), (it / C::NS) & 1);
+#endif
             ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
             if (!ok) break;
+            long long tn1 = PROF_T();
+            PROF_ADD(1, tn1 - tn0);
+#ifdef SSD_EXP_PROF
+            if (had_to_wait) { prof[4] += tn1 - t_issue[s]; prof[5] += 1; }
+#endif
             ok = mbar_wait(bar_bs_full(s), (it / C::NS) & 1, wc, kWaitBsFull);
             if (!ok) break;
+            long long tn2 = PROF_T();
+            PROF_ADD(2, tn2 - tn1);
             tc_fence_after();
             const uint64_t ad_t = adesc0 + (uint64_t)((s * C::STAGE_BYTES) >> 4);
             const uint64_t bd_s = bdesc0 + (uint64_t)((s * C::STAGE_BYTES) >> 4);
@@ -360,15 +402,22 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
               }
             }
             if (ok) mma_commit(bar_empty(s));
+            PROF_ADD(3, PROF_T() - tn2);
           }
           if (ok) mma_commit(bar_acc_full(buf));
         }
       }
+#ifdef SSD_EXP_PROF
+      prof[7] = clock64() - tstart;
+      for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 8 + i] = prof[i];
+#endif
     }
-  } else if (warp >= C::EPI_WARPS + 2) {
-    // ============================== B scaling =========================================
-    const int stid = tid - (C::EPI_WARPS + 2) * 32;
-    uint32_t it = 0, item = 0;
+  } else {
+    // ============================== scale vectors =====================================
+    // Two warps turn each chunk's dt / dA_cumsum rows into the per-position factors
+    // exp(min(a_last - a_k, 0)) * dt_k, one item ahead of the B-scaling warps.
+    const int vt = tid - (C::EPI_WARPS + 2) * 32;
+    uint32_t item = 0;
     bool ok = true;
     for (int j = 0; j < rg.m && ok; ++j) {
       int strip, c0, c1;
@@ -377,29 +426,60 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int r = item % C::ND;
         ok = mbar_wait(bar_dd_full(r), (item / C::ND) & 1, wc, kWaitDdFull);
         if (!ok) break;
+        if (item >= 2) {
+          ok = mbar_wait(bar_sc_free(item & 1), ((item >> 1) - 1) & 1, wc, kWaitGroup);
+          if (!ok) break;
+        }
         const float* dd = reinterpret_cast<const float*>(smem + C::OFF_DTDA + r * C::DTDA_SLOT);
         float* sc = reinterpret_cast<float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
 #pragma unroll
         for (int hd = 0; hd < HPC; ++hd) {
           const float* row = dd + hd * 2 * kMaxL;
           const float last = row[kMaxL + L - 1];
-          for (int k = stid; k < L; k += C::SCALE_THREADS) {
+          for (int k = vt; k < L; k += C::SCV_THREADS) {
             float d = last - row[kMaxL + k];
             if (a.clamp_decay) d = fminf(d, 0.0f);
             sc[hd * kMaxL + k] = fast_exp(d) * row[k];
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_sc_sync());
-        ok = mbar_wait(bar_sc_sync(), item & 1, wc, kWaitGroup);
+        if (lane == 0) {
+          mbar_arrive(bar_sc_ready(item & 1));
+          mbar_arrive(bar_dd_empty(r));
+        }
+      }
+    }
+  }
+  } else if (warp >= C::SCALE_WARP0) {
+    // ============================== B scaling =========================================
+    if constexpr (C::REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REGS_SCALE));
+    const int stid = tid - C::SCALE_WARP0 * 32;
+    uint32_t it = 0, item = 0;
+    bool ok = true;
+#ifdef SSD_EXP_PROF
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long tstart = clock64();
+#endif
+    for (int j = 0; j < rg.m && ok; ++j) {
+      int strip, c0, c1;
+      get_segment(rg, nchunks, j, strip, c0, c1);
+      for (int c = c0; c < c1 && ok; ++c, ++item) {
+        long long ts0 = PROF_T();
+        ok = mbar_wait(bar_sc_ready(item & 1), (item >> 1) & 1, wc, kWaitDdFull);
         if (!ok) break;
-        if (stid == 0) mbar_arrive(bar_dd_empty(r));
+        long long ts1 = PROF_T();
+        PROF_ADD(0, ts1 - ts0);
+        const float* sc = reinterpret_cast<const float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
+        PROF_ADD(1, PROF_T() - ts1);
         const int limit = min(L, a.seqlen - c * L);
         const int ksteps = (limit + kKT - 1) / kKT;
         for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
           const int s = it % C::NS;
+          long long tu0 = PROF_T();
           ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
           if (!ok) break;
+          long long tu1 = PROF_T();
+          PROF_ADD(2, tu1 - tu0);
           const uint8_t* raw = smem + C::OFF_STAGES + s * C::STAGE_BYTES;
           uint8_t* dst = smem + C::OFF_STAGES + s * C::STAGE_BYTES;
           const float* sch = sc + ks * kKT;
@@ -410,6 +490,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
           constexpr int kPerThread = (kChunks + C::SCALE_THREADS - 1) / C::SCALE_THREADS;
           const int vt = stid;
           uint4 v[kPerThread];
+#ifndef SSD_EXP_NOSCALE
 #pragma unroll
           for (int q = 0; q < kPerThread; ++q) {
             const int i = vt + q * C::SCALE_THREADS;
@@ -442,21 +523,100 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
               }
             }
           }
+#endif
+          long long tu2 = PROF_T();
+          PROF_ADD(3, tu2 - tu1);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_bs_full(s));
+          PROF_ADD(4, PROF_T() - tu2);
         }
+        // (the __syncwarp of the last stage ordered every lane's reads of the scale vector)
+        if (ok && lane == 0) mbar_arrive(bar_sc_free(item & 1));
       }
     }
+#ifdef SSD_EXP_PROF
+    if (stid == 0) {
+      prof[7] = clock64() - tstart;
+      for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 16 + i] = prof[i];
+    }
+#endif
   } else {
     // ============================== epilogue ==========================================
+    if constexpr (C::REBALANCE) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::REGS_EPI));
+    // One warpgroup per head; warp wq of it owns TMEM lanes 32 wq .. 32 wq + 31 (dstate n).
+    // Accumulators are read in the matrix-fragment arrangement (tmem_ld_16x256b_x4), which is
+    // also the arrangement stmatrix stores transposed: a warp builds its 32 rows x 32 columns of
+    // a 16-bit (p, n) tile in shared memory with four stmatrix and one lane sends it off with
+    // one TMA store.  Nothing here needs another warp.
+    // Element i (0..63) of a thread's fragment, with g = lane / 4 and qd = lane % 4:
+    //   n = 32 wq + 16 ((i / 16) % 2) + 8 ((i / 2) % 2) + g
+    //   p = 32 (i / 32) + 8 ((i / 4) % 4) + (i % 2) + 2 qd
     const int hd = warp >> 2;
-    const int n = (warp & 3) * 32 + lane;
-    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    constexpr int kEW = C::EPI_COLS;      // accumulator columns handled per TMEM load
+    const int wq = warp & 3;
+    const int nb = wq * 32 + (lane >> 2);
+    const int pb = 2 * (lane & 3);
+    auto fn = [](int i) { return ((i >> 4) & 1) * 16 + ((i >> 1) & 1) * 8; };
+    auto fp = [](int i) { return (i >> 5) * 32 + ((i >> 2) & 3) * 8 + (i & 1); };
+    const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t stg = sbase + C::OFF_STAGING + warp * C::STAGING_BYTES;
+    // This thread's row address for stmatrix: row (lane % 8) of matrix (lane / 8); matrices 0/1
+    // are the two 8-column blocks of one 8-row block, matrices 2/3 those of the next 8 rows.
+    // A staging row is 64 bytes = four 16-byte pieces; the 64-byte swizzle puts piece c of row r
+    // at piece c ^ ((r / 2) % 4), which for every row this thread addresses is (lane / 2) % 4.
+    const uint32_t stm_rows = stg + (((lane >> 4) & 1) * 8 + (lane & 7)) * 64;
+    const uint32_t stm_swz = (lane >> 1) & 3, stm_blk = (lane >> 3) & 1;
+    const uint32_t stm_row[2] = {stm_rows + ((stm_blk ^ stm_swz) << 4), stm_rows + (((2 + stm_blk) ^ stm_swz) << 4)};
     float S[kP];
     uint32_t item = 0, epi_syncs = 0;
     bool ok = true;
+#ifdef SSD_EXP_PROF
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long tstart = clock64();
+#endif
+    // Stores 32 rows (p = 32 hq ..) of a (kP x kN) tile whose element (0, 0) is at element
+    // offset `tile` of `base`, row pitch `pitch`, from the fragment values vals[0..31].
+    // `map` != nullptr: 16-bit tile (b = cb, chunk = cc, head = ch) of the tensor behind the map.
+    auto store_half = [&](void* base, int dtype, int64_t tile, int64_t pitch, int hq, const float (&vals)[32],
+                          const CUtensorMap* map, int cb, int cc, int ch) {
+      if (map == nullptr) {
+        const int64_t e0 = tile + (int64_t)(hq * 32 + pb) * pitch + nb;
+        if (dtype == SSD_F32) {
+          float* o = static_cast<float*>(base) + e0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[(int64_t)fp(i) * pitch + fn(i)] = vals[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) store_f(base, dtype, e0 + (int64_t)fp(i) * pitch + fn(i), vals[i]);
+        }
+        return;
+      }
+      uint32_t pk[16];
+      if (dtype == SSD_BF16) {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) pk[k] = Pack<__nv_bfloat16>::pack(vals[2 * k], vals[2 * k + 1]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) pk[k] = Pack<__half>::pack(vals[2 * k], vals[2 * k + 1]);
+      }
+      // the previous TMA store of this warp has read the staging rows
+      if (lane == 0) bulk_wait_read_all();
+      __syncwarp();
+#pragma unroll
+      for (int lh = 0; lh < 2; ++lh)
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp)
+          stmatrix_x4_trans(stm_row[lh] + jp * 16 * 64, pk[lh * 8 + 4 * jp], pk[lh * 8 + 4 * jp + 1],
+                            pk[lh * 8 + 4 * jp + 2], pk[lh * 8 + 4 * jp + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+#ifndef SSD_EXP_NOSTORE
+        tma_store_5d(map, stg, wq * 32, hq * 32, ch, cc, cb);
+#endif
+        bulk_commit();
+      }
+    };
     for (int j = 0; j < rg.m && ok; ++j) {
       int strip, c0, c1;
       get_segment(rg, nchunks, j, strip, c0, c1);
@@ -465,23 +625,23 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (a.mode == 0) {
         if (c0 == 0) {
           if (a.init != nullptr) {
-            const int64_t ib = (int64_t)b * a.init_s[0] + (int64_t)h * a.init_s[1] + n;
+            const int64_t ib = (int64_t)b * a.init_s[0] + (int64_t)h * a.init_s[1] + (int64_t)pb * a.init_s[2] + nb;
 #pragma unroll
-            for (int p = 0; p < kP; ++p) S[p] = load_f(a.init, a.init_dtype, ib + (int64_t)p * a.init_s[2]);
+            for (int i = 0; i < kP; ++i) S[i] = load_f(a.init, a.init_dtype, ib + (int64_t)fp(i) * a.init_s[2] + fn(i));
           } else {
 #pragma unroll
-            for (int p = 0; p < kP; ++p) S[p] = 0.0f;
+            for (int i = 0; i < kP; ++i) S[i] = 0.0f;
           }
         } else if (a.defer) {
 #pragma unroll
-          for (int p = 0; p < kP; ++p) S[p] = 0.0f;
+          for (int i = 0; i < kP; ++i) S[i] = 0.0f;
         } else {
           const int src = (int)blockIdx.x - 1;
           ok = flag_wait(a.flags + (size_t)src * HPC + hd, epoch_target, wc, kWaitCarry);
           if (!ok) break;
-          const float* cin = a.carry + ((size_t)src * HPC + hd) * (kP * kN) + n;
+          const float* cin = a.carry + ((size_t)src * HPC + hd) * (kP * kN) + pb * kN + nb;
 #pragma unroll
-          for (int p = 0; p < kP; ++p) S[p] = __ldcg(cin + p * kN);
+          for (int i = 0; i < kP; ++i) S[i] = __ldcg(cin + fp(i) * kN + fn(i));
         }
       }
       for (int c = c0; c < c1 && ok; ++c, ++item) {
@@ -489,49 +649,56 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
         float decay = 0.0f;
         if (a.mode == 0)
           decay = fast_exp(__ldg(a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2] + (L - 1)));
+        long long te0 = PROF_T();
         ok = mbar_wait(bar_acc_full(buf), (item / C::NBUF) & 1, wc, kWaitAccFull, 128);
         if (!ok) break;
+        long long te1 = PROF_T();
+        PROF_ADD(0, te1 - te0);
         tc_fence_after();
         const uint32_t taddr = tmem_base + lane_sel + (hd * C::NBUF + buf) * kP;
 #pragma unroll
-        for (int q = 0; q < kP / kEW; ++q) {
-          uint32_t raw[kEW];
-          tmem_ld_32xN(taddr + q * kEW, raw);
+        for (int hq = 0; hq < 2; ++hq) {
+          uint32_t raw_lo[16], raw_hi[16];
+          tmem_ld_16x256b_x4(taddr + hq * 32, raw_lo);
+          tmem_ld_16x256b_x4(taddr + (16u << 16) + hq * 32, raw_hi);
           tmem_ld_wait();
-          if (q == kP / kEW - 1) {
+          if (hq == 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_empty(hd, buf));
           }
-          float v[kEW];
+          float v[32];
 #pragma unroll
-          for (int i = 0; i < kEW; ++i) v[i] = __uint_as_float(raw[i]);
+          for (int i = 0; i < 16; ++i) {
+            v[i] = __uint_as_float(raw_lo[i]);
+            v[16 + i] = __uint_as_float(raw_hi[i]);
+          }
           if (a.states != nullptr) {
-            const int64_t so = (int64_t)b * a.states_s[0] + (int64_t)c * a.states_s[1] + (int64_t)h * a.states_s[2] +
-                               (int64_t)(q * kEW) * a.states_s[3];
-            store_rows<kEW>(a.states, a.states_dtype, so, a.states_s[3], n, v);
+            const int64_t so = (int64_t)b * a.states_s[0] + (int64_t)c * a.states_s[1] + (int64_t)h * a.states_s[2];
+            store_half(a.states, a.states_dtype, so, a.states_s[3], hq, v, nullptr, 0, 0, 0);
           }
           if (a.mode == 0) {
-            float cur[kEW];
+            float cur[32];
 #pragma unroll
-            for (int i = 0; i < kEW; ++i) cur[i] = S[q * kEW + i];
-            const int64_t oo = (int64_t)b * a.out_s[0] + (int64_t)c * a.out_s[1] + (int64_t)h * a.out_s[2] +
-                               (int64_t)(q * kEW) * a.out_s[3];
-            store_rows<kEW, OUT32 ? 32 : 16>(a.out, a.out_dtype, oo, a.out_s[3], n, cur);
+            for (int i = 0; i < 32; ++i) cur[i] = S[hq * 32 + i];
+            const int64_t oo = (int64_t)b * a.out_s[0] + (int64_t)c * a.out_s[1] + (int64_t)h * a.out_s[2];
+            store_half(a.out, OUT32 ? (int)SSD_F32 : a.out_dtype, oo, a.out_s[3], hq, cur, OUT32 ? nullptr : &tmap_out, b,
+                       c, h);
 #pragma unroll
-            for (int i = 0; i < kEW; ++i) S[q * kEW + i] = fmaf(decay, cur[i], v[i]);
+            for (int i = 0; i < 32; ++i) S[hq * 32 + i] = fmaf(decay, cur[i], v[i]);
           }
         }
+        PROF_ADD(1, PROF_T() - te1);
       }
       if (!ok || a.mode != 0) continue;
       if (c1 == nchunks) {
-        float* fo = a.final_states + (int64_t)b * a.final_s[0] + (int64_t)h * a.final_s[1] + n;
+        float* fo = a.final_states + (int64_t)b * a.final_s[0] + (int64_t)h * a.final_s[1] + (int64_t)pb * a.final_s[2] + nb;
 #pragma unroll
-        for (int p = 0; p < kP; ++p) fo[(int64_t)p * a.final_s[2]] = S[p];
+        for (int i = 0; i < kP; ++i) fo[(int64_t)fp(i) * a.final_s[2] + fn(i)] = S[i];
       } else {
-        float* co = a.carry + ((size_t)blockIdx.x * HPC + hd) * (kP * kN) + n;
+        float* co = a.carry + ((size_t)blockIdx.x * HPC + hd) * (kP * kN) + pb * kN + nb;
 #pragma unroll
-        for (int p = 0; p < kP; ++p) __stcg(co + p * kN, S[p]);
+        for (int i = 0; i < kP; ++i) __stcg(co + fp(i) * kN + fn(i), S[i]);
         __threadfence();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_epi_sync(hd));
@@ -541,6 +708,13 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if ((tid & 127) == 0) st_release_gpu(a.flags + (size_t)blockIdx.x * HPC + hd, epoch_target);
       }
     }
+    bulk_wait_all();            // this thread's bulk copies are complete before the CTA retires
+#ifdef SSD_EXP_PROF
+    if (tid == 0) {
+      prof[7] = clock64() - tstart;
+      for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 24 + i] = prof[i];
+    }
+#endif
   }
 
   // ================================ teardown ==========================================
@@ -681,6 +855,23 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int inner, int heads
   return SSD_OK;
 }
 
+// 5-D map over the 16-bit passed states (b, c, h, p, n) with (p, n) dense; box = 32 columns (one
+// epilogue warp's dstate quadrant) x 32 rows, 64-byte swizzle.
+int make_out_map(CUtensorMap* map, void* base, int dtype, int nheads, int nchunks, int batch, const int64_t* stride) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[5] = {(cuuint64_t)kN, (cuuint64_t)kP, (cuuint64_t)nheads, (cuuint64_t)nchunks, (cuuint64_t)batch};
+  const cuuint64_t strides[4] = {(cuuint64_t)stride[3] * 2, (cuuint64_t)stride[2] * 2, (cuuint64_t)stride[1] * 2,
+                                 (cuuint64_t)stride[0] * 2};
+  const cuuint32_t box[5] = {32, 32, 1, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 5, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled (out) failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int num_sms() {
@@ -705,6 +896,12 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   if (rc != SSD_OK) return rc;
   rc = make_map(&mB, in.B, in.in_dtype, kN, in.ngroups, in.seqlen, in.batch, in.B_stride);
   if (rc != SSD_OK) return rc;
+  CUtensorMap mo = mx;                  // a valid map even where the kernel never touches it
+  if (mode == 0 && p.out_dtype != SSD_F32) {
+    rc = make_out_map(&mo, p.out, p.out_dtype, in.nheads, (in.seqlen + in.chunk_size - 1) / in.chunk_size, in.batch,
+                      p.out_stride);
+    if (rc != SSD_OK) return rc;
+  }
 
   FusedArgs a{};
   a.dt = in.dt;
@@ -758,7 +955,7 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   // keeps the passed states free of the second rounding that a later correction implies.)
   const long long per_cta = (total + grid - 1) / grid;
   a.defer = (mode == 0 && a.nchunks > per_cta && per_cta >= 16) ? 1 : 0;
-  kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(mx, mB, a);
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(mx, mB, mo, a);
   SSD_CUDA_OK(cudaGetLastError());
   if (a.defer) {
     SegFixArgs f{};
@@ -787,6 +984,12 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
 
 }  // namespace
 
+#ifdef SSD_EXP_PROF
+extern "C" __attribute__((visibility("default"))) int ssd_debug_read_prof(long long* dst, int n) {
+  return (int)cudaMemcpyFromSymbol(dst, g_prof, sizeof(long long) * n);
+}
+#endif
+
 int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why) {
   const ssd_state_inputs_t& in = p.in;
   auto no = [&](const char* m) { if (why) *why = m; return 0; };
@@ -806,9 +1009,11 @@ int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why) {
     if (ptr == nullptr) return true;
     if (s[ns - 1] != kN) return false;                      // (p, n) contiguous
     if ((reinterpret_cast<uintptr_t>(ptr) & 3) != 0) return false;
-    if (dtype != SSD_F32)
+    if (dtype != SSD_F32) {                                 // rows leave through 16-byte bulk copies
+      if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return false;
       for (int i = 0; i < ns; ++i)
-        if (s[i] % 2 != 0) return false;                    // packed pair stores
+        if (s[i] % 8 != 0) return false;
+    }
     return true;
   };
   if (!rows_ok(p.out, p.out_dtype, p.out_stride, 4)) return no("out layout");
