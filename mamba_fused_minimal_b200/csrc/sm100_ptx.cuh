@@ -232,8 +232,41 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t adesc, uint
 }
 // The mbarrier gets one arrival when every tcgen05 operation issued so far by this thread
 // has completed.
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (M rows on the lanes, two 16-bit K
+// elements per 32-bit column) was written to tensor memory with tcgen05.st.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+// Store to 16 lanes x 16 columns in the 16x128b arrangement: with g = thread / 4, q = thread % 4,
+// registers 2i and 2i + 1 go to column 4i + q of lanes L0 + g and L0 + g + 8 (L0 = lane field of
+// the address, 0 or 16 inside the warp's 32 lanes).
+__device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// Four 8x8 matrices of 16-bit elements, loaded transposed: register i of thread t receives
+// elements (row 2 * (t % 4), column t / 4) and (row 2 * (t % 4) + 1, column t / 4) of matrix i,
+// low half first; thread t supplies the address of row t % 8 of matrix t / 8 (16 bytes).
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t row_addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(row_addr)
                : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {

@@ -55,40 +55,52 @@ enum WaitCode {
 
 template <int HPC>
 struct Cfg {
-  static constexpr int NS = (HPC == 1) ? 6 : 4;       // pipeline stages (TMA -> scale in place -> MMA)
-  static constexpr int NT = NS;                       // one 'scaled' barrier per stage
+  static constexpr int NS = 6;                        // shared-memory stages (raw B tile + x tiles)
+  static constexpr int NA = 2;                        // scaled-B (A operand) slots per head in TMEM
   static constexpr int ND = 2;                        // dt/dA row slots
-  static constexpr int NBUF = 4;                      // TMEM accumulators per head
+  static constexpr int NBUF = (HPC == 2) ? 3 : 4;     // TMEM accumulators per head
   static constexpr int EPI_WARPS = 4 * HPC;
-#ifndef SSD_SCALE_WARPS
-#define SSD_SCALE_WARPS 8
-#endif
-  static constexpr int SCALE_WARPS = SSD_SCALE_WARPS;
-  // one warpgroup of service warps: TMA producer, MMA issuer, two scale-vector warps
+  // B-scaling warps: a warp can only write the TMEM lanes of its quadrant (warp index % 4), so
+  // four quadrants x two halves of a stage's 64 positions
+  static constexpr int SCALE_WARPS = 8;
+  // one warpgroup of service warps: TMA producer, one MMA issuer per head (the second idles at
+  // HPC = 1), the scale-vector warp
   static constexpr int SERVICE_WARPS = 4;
-  static constexpr int SCV_THREADS = 64;
   static constexpr int SCALE_WARP0 = EPI_WARPS + SERVICE_WARPS;
   static constexpr int WARPS = SCALE_WARP0 + SCALE_WARPS;
   static constexpr int THREADS = WARPS * 32;
   static constexpr int SCALE_THREADS = SCALE_WARPS * 32;
   static constexpr int RAWB_BYTES = kKT * kN * 2;     // 16 KiB: two 64-column SW128 boxes
   static constexpr int X_BYTES = kKT * kP * 2;        // 8 KiB: one SW128 box
-  // a stage: the raw B tile (scaled IN PLACE into the last head's A operand), one more A tile
-  // per further head, then one x tile per head
+  // a stage: the raw B tile, then one x tile per head
   static constexpr int LOAD_BYTES = RAWB_BYTES + HPC * X_BYTES;   // what TMA brings per stage
-  static constexpr int OFF_XT = HPC * RAWB_BYTES;                 // x tiles inside a stage
-  static constexpr int STAGE_BYTES = HPC * RAWB_BYTES + HPC * X_BYTES;
-  static constexpr int TMEM_COLS = HPC * NBUF * kP;   // 256 or 512
+  static constexpr int OFF_XT = RAWB_BYTES;                       // x tiles inside a stage
+  static constexpr int STAGE_BYTES = LOAD_BYTES;
+  // tensor memory: NBUF accumulators of kP columns per head, then NA scaled-B slots of kKT / 2
+  // columns per head (two 16-bit K elements per column)
+  static constexpr int TMEM_A0 = HPC * NBUF * kP;
+  static constexpr int A_COLS = kKT / 2;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(TMEM_A0 + HPC * NA * A_COLS <= TMEM_COLS, "tensor memory budget");
   // shared-memory map (byte offsets from a 1024-aligned base)
   static constexpr int OFF_STAGES = 0;
   static constexpr int OFF_DTDA = OFF_STAGES + NS * STAGE_BYTES;
-  // A-operand tile of head hd inside a stage: the last head reuses the raw tile's place
-  __host__ __device__ static constexpr int a_tile_off(int hd) { return hd == HPC - 1 ? 0 : (1 + hd) * RAWB_BYTES; }
   static constexpr int DTDA_SLOT = HPC * 2 * kMaxL * 4;
   static constexpr int OFF_SCALE = OFF_DTDA + ND * DTDA_SLOT;
   static constexpr int SCALE_SLOT = HPC * kMaxL * 4;
   static constexpr int OFF_BARS = OFF_SCALE + 2 * SCALE_SLOT;
-  static constexpr int NUM_BARS = 2 * NS + 2 * NT + 2 * ND + NBUF + HPC * NBUF + 4 + HPC;
+  // mbarrier indices
+  static constexpr int B_FULL = 0;                       // [NS]  stage loaded (TMA bytes)
+  static constexpr int B_EMPTY = B_FULL + NS;            // [NS]  stage consumed (one commit per MMA issuer)
+  static constexpr int B_BS = B_EMPTY + NS;              // [NA]  scaled B written (one arrival per scaling warp)
+  static constexpr int B_AFREE = B_BS + NA;              // [NA]  scaled B consumed (one commit per MMA issuer)
+  static constexpr int B_DD = B_AFREE + NA;              // [ND]  dt / dA rows loaded
+  static constexpr int B_ACCF = B_DD + ND;               // [HPC][NBUF] accumulator complete
+  static constexpr int B_ACCE = B_ACCF + HPC * NBUF;     // [HPC][NBUF] accumulator drained (4 epilogue warps)
+  static constexpr int B_SCR = B_ACCE + HPC * NBUF;      // [2]   scale vector ready
+  static constexpr int B_SCF = B_SCR + 2;                // [2]   scale vector no longer needed
+  static constexpr int B_EPI = B_SCF + 2;                // [HPC] epilogue warpgroup sync
+  static constexpr int NUM_BARS = B_EPI + HPC;
   static constexpr int OFF_CTL = OFF_BARS + NUM_BARS * 8;
   // staging for 16-bit passed states: every epilogue warp owns 32 rows (p) x 32 columns (its
   // dstate quadrant) = 32 x 64 bytes, laid out as a TMA box with the 64-byte swizzle
@@ -216,36 +228,28 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
 
   // barrier addresses
   const uint32_t bars = sbase + C::OFF_BARS;
-  auto bar_full = [&](int s) { return bars + 8u * s; };
-  auto bar_empty = [&](int s) { return bars + 8u * (C::NS + s); };
-  auto bar_bs_full = [&](int t) { return bars + 8u * (2 * C::NS + t); };
-  auto bar_dd_full = [&](int r) { return bars + 8u * (2 * C::NS + 2 * C::NT + r); };
-  auto bar_dd_empty = [&](int r) { return bars + 8u * (2 * C::NS + 2 * C::NT + C::ND + r); };
-  auto bar_acc_full = [&](int b) { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + b); };
-  auto bar_acc_empty = [&](int hd, int b) {
-    return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + hd * C::NBUF + b);
-  };
-  // group barriers (an mbarrier instead of bar.sync so that the wait is bounded like the rest)
-  // scale-vector slots (two, alternating by item): filled by the scale-vector warps, read by
-  // the B-scaling warps
-  auto bar_sc_ready = [&](int i) { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF + i); };
-  auto bar_sc_free = [&](int i) { return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF + 2 + i); };
-  auto bar_epi_sync = [&](int hd) {
-    return bars + 8u * (2 * C::NS + 2 * C::NT + 2 * C::ND + C::NBUF + HPC * C::NBUF + 4 + hd);
-  };
+  auto bar_full = [&](int s) { return bars + 8u * (C::B_FULL + s); };
+  auto bar_empty = [&](int s) { return bars + 8u * (C::B_EMPTY + s); };
+  auto bar_bs_full = [&](int t) { return bars + 8u * (C::B_BS + t); };
+  auto bar_a_free = [&](int t) { return bars + 8u * (C::B_AFREE + t); };
+  auto bar_dd_full = [&](int r) { return bars + 8u * (C::B_DD + r); };
+  auto bar_acc_full = [&](int hd, int b) { return bars + 8u * (C::B_ACCF + hd * C::NBUF + b); };
+  auto bar_acc_empty = [&](int hd, int b) { return bars + 8u * (C::B_ACCE + hd * C::NBUF + b); };
+  auto bar_sc_ready = [&](int i) { return bars + 8u * (C::B_SCR + i); };
+  auto bar_sc_free = [&](int i) { return bars + 8u * (C::B_SCF + i); };
+  // (an mbarrier instead of bar.sync so that the wait is bounded like the rest)
+  auto bar_epi_sync = [&](int hd) { return bars + 8u * (C::B_EPI + hd); };
   volatile int* ctl = reinterpret_cast<volatile int*>(smem + C::OFF_CTL);   // [0] abort, [1] tmem, [2] epoch
   WaitCtx wc{ctl, a.status};
 
   if (tid == 0) {
-    for (int s = 0; s < C::NS; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-    for (int t = 0; t < C::NT; ++t) mbar_init(bar_bs_full(t), C::SCALE_WARPS);
-    for (int r = 0; r < C::ND; ++r) { mbar_init(bar_dd_full(r), 1); mbar_init(bar_dd_empty(r), C::SCV_THREADS / 32); }
-    for (int b = 0; b < C::NBUF; ++b) {
-      mbar_init(bar_acc_full(b), 1);
-      for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_acc_empty(hd, b), 4);
-    }
+    for (int s = 0; s < C::NS; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), HPC); }
+    for (int t = 0; t < C::NA; ++t) { mbar_init(bar_bs_full(t), C::SCALE_WARPS); mbar_init(bar_a_free(t), HPC); }
+    for (int r = 0; r < C::ND; ++r) mbar_init(bar_dd_full(r), 1);
+    for (int hd = 0; hd < HPC; ++hd)
+      for (int b = 0; b < C::NBUF; ++b) { mbar_init(bar_acc_full(hd, b), 1); mbar_init(bar_acc_empty(hd, b), 4); }
     // group barriers take ONE arrival per warp: arrivals on one mbarrier serialise
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_sc_ready(i), C::SCV_THREADS / 32); mbar_init(bar_sc_free(i), C::SCALE_WARPS); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_sc_ready(i), 1); mbar_init(bar_sc_free(i), C::SCALE_WARPS); }
     for (int hd = 0; hd < HPC; ++hd) mbar_init(bar_epi_sync(hd), 4);
     ctl[0] = 0;
     ctl[2] = reinterpret_cast<volatile int*>(a.status)[1];     // epoch of the previous launch
@@ -274,186 +278,187 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   const int ratio = a.nheads / a.ngroups;
 
   if (warp >= C::EPI_WARPS && warp < C::SCALE_WARP0) {
-  if constexpr (C::REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REGS_SERVICE));
-  if (warp == C::EPI_WARPS) {
-    // ============================== TMA producer ======================================
-    if (lane == 0) {
-      // B is read once per head of its group and should stay in L2 between those reads;
-      // x is read exactly once.
-      const uint64_t keep = l2_policy_evict_last(), stream_once = l2_policy_evict_first();
-      uint32_t it = 0, item = 0;
-      bool ok = true;
+    if constexpr (C::REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REGS_SERVICE));
+    if (warp == C::EPI_WARPS) {
+      // ============================== TMA producer ====================================
+      if (lane == 0) {
+        // B is read once per head of its group and should stay in L2 between those reads;
+        // x is read exactly once.
+        const uint64_t keep = l2_policy_evict_last(), stream_once = l2_policy_evict_first();
+        uint32_t it = 0;
+        bool ok = true;
+        for (int j = 0; j < rg.m && ok; ++j) {
+          int strip, c0, c1;
+          get_segment(rg, nchunks, j, strip, c0, c1);
+          const int b = strip / a.strips_per_batch;
+          const int h0 = (strip % a.strips_per_batch) * HPC;
+          const int g = h0 / ratio;
+          for (int c = c0; c < c1 && ok; ++c) {
+            const int limit = min(L, a.seqlen - c * L);
+            const int ksteps = (limit + kKT - 1) / kKT;
+            for (int ks = 0; ks < ksteps; ++ks, ++it) {
+              const int s = it % C::NS;
+              ok = mbar_wait(bar_empty(s), ((it / C::NS) & 1) ^ 1, wc, kWaitStageEmpty);
+              if (!ok) break;
+              mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
+              const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
+              const int l0 = c * L + ks * kKT;
+              tma_load_4d_hint(st, &tmap_B, bar_full(s), 0, g, l0, b, keep);
+              tma_load_4d_hint(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b, keep);
+#pragma unroll
+              for (int hd = 0; hd < HPC; ++hd)
+                tma_load_4d_hint(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b, stream_once);
+            }
+          }
+        }
+      }
+    } else if (warp <= C::EPI_WARPS + HPC) {
+      // ============================== MMA issuer of head mhd ==========================
+      // One issuing thread per head: the two heads' accumulators are independent, and two
+      // threads keep the tensor pipe fed where one spent half its time issuing.
+      const int mhd = warp - (C::EPI_WARPS + 1);
+      if (lane == 0) {
+        // A (the scaled B tile) comes from tensor memory, K-major by construction; B (the x
+        // tile) from shared memory as TMA delivered it: headdim contiguous, i.e. MN-major.
+        constexpr uint32_t idesc = mma_idesc(Pack<T>::kFmt, false, true, kN, kP);
+        // Descriptor of stage 0; the address field (bits 0-13, units of 16 bytes) never carries
+        // out of its field for shared-memory addresses below 256 KiB, so other stages and
+        // k-steps are reached by plain 64-bit additions.
+        const uint64_t bdesc0 = smem_desc_sw128(sbase + C::OFF_STAGES + C::OFF_XT + mhd * C::X_BYTES, C::X_BYTES, 1024);
+        uint32_t it = 0, item = 0;
+        bool ok = true;
 #ifdef SSD_EXP_PROF
-      long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      volatile long long* t_issue = reinterpret_cast<volatile long long*>(smem + C::OFF_CTL + 16);
-      const long long tstart = clock64();
+        long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const long long tstart = clock64();
 #endif
-      for (int j = 0; j < rg.m && ok; ++j) {
-        int strip, c0, c1;
-        get_segment(rg, nchunks, j, strip, c0, c1);
+        for (int j = 0; j < rg.m && ok; ++j) {
+          int strip, c0, c1;
+          get_segment(rg, nchunks, j, strip, c0, c1);
+          for (int c = c0; c < c1 && ok; ++c, ++item) {
+            const int buf = item % C::NBUF;
+            long long tm0 = PROF_T();
+            ok = mbar_wait(bar_acc_empty(mhd, buf), ((item / C::NBUF) & 1) ^ 1, wc, kWaitAccEmpty);
+            if (!ok) break;
+            PROF_ADD(0, PROF_T() - tm0);
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (mhd * C::NBUF + buf) * kP;
+            const int limit = min(L, a.seqlen - c * L);
+            const int ksteps = (limit + kKT - 1) / kKT;
+            for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+              const int s = it % C::NS;
+              const int sa = it % C::NA;
+              long long tn0 = PROF_T();
+              ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
+              if (!ok) break;
+              long long tn1 = PROF_T();
+              PROF_ADD(1, tn1 - tn0);
+              ok = mbar_wait(bar_bs_full(sa), (it / C::NA) & 1, wc, kWaitBsFull);
+              if (!ok) break;
+              long long tn2 = PROF_T();
+              PROF_ADD(2, tn2 - tn1);
+              tc_fence_after();
+              const uint64_t bd_s = bdesc0 + (uint64_t)((s * C::STAGE_BYTES) >> 4);
+              const uint32_t a_tmem = tmem_base + C::TMEM_A0 + (mhd * C::NA + sa) * C::A_COLS;
+#pragma unroll
+              for (int k16 = 0; k16 < kKT / 16; ++k16)
+                mma_f16_ts(d_tmem, a_tmem + k16 * 8, bd_s + (uint64_t)((k16 * 2048) >> 4), idesc, (ks | k16) != 0 ? 1u : 0u);
+              mma_commit(bar_a_free(sa));
+              mma_commit(bar_empty(s));
+              PROF_ADD(3, PROF_T() - tn2);
+            }
+            if (ok) mma_commit(bar_acc_full(mhd, buf));
+          }
+        }
+#ifdef SSD_EXP_PROF
+        if (mhd == 0) {
+          prof[7] = clock64() - tstart;
+          for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 8 + i] = prof[i];
+        }
+#endif
+      }
+    } else if (warp == C::EPI_WARPS + 3) {
+      // ============================== scale vectors ===================================
+      // One warp loads each chunk's dt / dA_cumsum rows (bulk copies, ND chunks ahead) and turns
+      // them into the per-position factors exp(min(a_last - a_k, 0)) * dt_k, one item ahead of
+      // the B-scaling warps.
+      auto load_rows = [&](int strip, int c, int slot) {          // one lane
         const int b = strip / a.strips_per_batch;
         const int h0 = (strip % a.strips_per_batch) * HPC;
-        const int g = h0 / ratio;
-        for (int c = c0; c < c1 && ok; ++c, ++item) {
-          const int r = item % C::ND;
-          long long tp0 = PROF_T();
-          ok = mbar_wait(bar_dd_empty(r), ((item / C::ND) & 1) ^ 1, wc, kWaitDdEmpty);
-          if (!ok) break;
-          long long tp1 = PROF_T();
-          PROF_ADD(0, tp1 - tp0);
-          mbar_expect_tx(bar_dd_full(r), HPC * 2 * L * 4);
+        mbar_expect_tx(bar_dd_full(slot), HPC * 2 * L * 4);
 #pragma unroll
-          for (int hd = 0; hd < HPC; ++hd) {
-            const uint32_t dst = sbase + C::OFF_DTDA + r * C::DTDA_SLOT + hd * 2 * kMaxL * 4;
-            bulk_load(dst, a.dt + (int64_t)b * a.dt_s[0] + (int64_t)(h0 + hd) * a.dt_s[1] + (int64_t)c * a.dt_s[2],
-                      L * 4, bar_dd_full(r));
-            bulk_load(dst + kMaxL * 4, a.dA + (int64_t)b * a.dA_s[0] + (int64_t)(h0 + hd) * a.dA_s[1] + (int64_t)c * a.dA_s[2],
-                      L * 4, bar_dd_full(r));
-          }
-          const int limit = min(L, a.seqlen - c * L);
-          const int ksteps = (limit + kKT - 1) / kKT;
-          PROF_ADD(1, PROF_T() - tp1);
-          for (int ks = 0; ks < ksteps; ++ks, ++it) {
-            const int s = it % C::NS;
-            long long tq0 = PROF_T();
-            ok = mbar_wait(bar_empty(s), ((it / C::NS) & 1) ^ 1, wc, kWaitStageEmpty);
-            if (!ok) break;
-            long long tq1 = PROF_T();
-            PROF_ADD(2, tq1 - tq0);
-#ifdef SSD_EXP_PROF
-            t_issue[s] = tq1;
-#endif
-            mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
-            const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
-            const int l0 = c * L + ks * kKT;
-            tma_load_4d_hint(st, &tmap_B, bar_full(s), 0, g, l0, b, keep);
-            tma_load_4d_hint(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b, keep);
-#pragma unroll
-            for (int hd = 0; hd < HPC; ++hd)
-              tma_load_4d_hint(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b, stream_once);
-            PROF_ADD(3, PROF_T() - tq1);
-          }
+        for (int hd = 0; hd < HPC; ++hd) {
+          const uint32_t dst = sbase + C::OFF_DTDA + slot * C::DTDA_SLOT + hd * 2 * kMaxL * 4;
+          bulk_load(dst, a.dt + (int64_t)b * a.dt_s[0] + (int64_t)(h0 + hd) * a.dt_s[1] + (int64_t)c * a.dt_s[2], L * 4,
+                    bar_dd_full(slot));
+          bulk_load(dst + kMaxL * 4, a.dA + (int64_t)b * a.dA_s[0] + (int64_t)(h0 + hd) * a.dA_s[1] + (int64_t)c * a.dA_s[2],
+                    L * 4, bar_dd_full(slot));
         }
+      };
+      // look-ahead position in the CTA's item order
+      int pj = 0, pstrip = 0, pc = 0, pc1 = 0;
+      if (rg.m > 0) get_segment(rg, nchunks, 0, pstrip, pc, pc1);
+      auto pre_valid = [&]() { return pj < rg.m; };
+      auto pre_next = [&]() {
+        if (++pc >= pc1 && ++pj < rg.m) get_segment(rg, nchunks, pj, pstrip, pc, pc1);
+      };
+      for (int i = 0; i < C::ND && pre_valid(); ++i) {
+        if (lane == 0) load_rows(pstrip, pc, i);
+        pre_next();
       }
-#ifdef SSD_EXP_PROF
-      prof[7] = clock64() - tstart;
-      for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + i] = prof[i];
-#endif
-    }
-  } else if (warp == C::EPI_WARPS + 1) {
-    // ============================== MMA issuer ========================================
-    if (lane == 0) {
-      constexpr uint32_t idesc = mma_idesc(Pack<T>::kFmt, true, true, kN, kP);
-      // Descriptors of slot 0 / stage 0, head 0; the address field (bits 0-13, units of
-      // 16 bytes) never carries out of its field for shared-memory addresses below 256 KiB,
-      // so other slots, heads and k-steps are reached by plain 64-bit additions.
-      const uint64_t adesc0 = smem_desc_sw128(sbase + C::OFF_STAGES, C::RAWB_BYTES / 2, 1024);
-      const uint64_t bdesc0 = smem_desc_sw128(sbase + C::OFF_STAGES + C::OFF_XT, C::X_BYTES, 1024);
-      uint32_t it = 0, item = 0;
+      uint32_t item = 0;
       bool ok = true;
-#ifdef SSD_EXP_PROF
-      long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      volatile long long* t_issue = reinterpret_cast<volatile long long*>(smem + C::OFF_CTL + 16);
-      const long long tstart = clock64();
-#endif
       for (int j = 0; j < rg.m && ok; ++j) {
         int strip, c0, c1;
         get_segment(rg, nchunks, j, strip, c0, c1);
         for (int c = c0; c < c1 && ok; ++c, ++item) {
-          const int buf = item % C::NBUF;
-          long long tm0 = PROF_T();
+          const int r = item % C::ND;
+          ok = mbar_wait(bar_dd_full(r), (item / C::ND) & 1, wc, kWaitDdFull);
+          if (!ok) break;
+          if (item >= 2) {
+            ok = mbar_wait(bar_sc_free(item & 1), ((item >> 1) - 1) & 1, wc, kWaitGroup);
+            if (!ok) break;
+          }
+          const float* dd = reinterpret_cast<const float*>(smem + C::OFF_DTDA + r * C::DTDA_SLOT);
+          float* sc = reinterpret_cast<float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
 #pragma unroll
           for (int hd = 0; hd < HPC; ++hd) {
-            if (ok) ok = mbar_wait(bar_acc_empty(hd, buf), ((item / C::NBUF) & 1) ^ 1, wc, kWaitAccEmpty);
-          }
-          if (!ok) break;
-          PROF_ADD(0, PROF_T() - tm0);
-          tc_fence_after();
-          const int limit = min(L, a.seqlen - c * L);
-          const int ksteps = (limit + kKT - 1) / kKT;
-          for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
-            const int s = it % C::NS;
-            long long tn0 = PROF_T();
-#ifdef SSD_EXP_PROF
-            const bool had_to_wait = !mbar_test_wait(bar_full(s), (it / C::NS) & 1);
-#endif
-            ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
-            if (!ok) break;
-            long long tn1 = PROF_T();
-            PROF_ADD(1, tn1 - tn0);
-#ifdef SSD_EXP_PROF
-            if (had_to_wait) { prof[4] += tn1 - t_issue[s]; prof[5] += 1; }
-#endif
-            ok = mbar_wait(bar_bs_full(s), (it / C::NS) & 1, wc, kWaitBsFull);
-            if (!ok) break;
-            long long tn2 = PROF_T();
-            PROF_ADD(2, tn2 - tn1);
-            tc_fence_after();
-            const uint64_t ad_t = adesc0 + (uint64_t)((s * C::STAGE_BYTES) >> 4);
-            const uint64_t bd_s = bdesc0 + (uint64_t)((s * C::STAGE_BYTES) >> 4);
-#pragma unroll
-            for (int hd = 0; hd < HPC; ++hd) {
-              const uint32_t d_tmem = tmem_base + (hd * C::NBUF + buf) * kP;
-#pragma unroll
-              for (int k16 = 0; k16 < kKT / 16; ++k16) {
-                const uint64_t ad = ad_t + (uint64_t)((C::a_tile_off(hd) + k16 * 2048) >> 4);
-                const uint64_t bd = bd_s + (uint64_t)((hd * C::X_BYTES + k16 * 2048) >> 4);
-                mma_f16_ss(d_tmem, ad, bd, idesc, (ks | k16) != 0 ? 1u : 0u);
-              }
+            const float* row = dd + hd * 2 * kMaxL;
+            const float last = row[kMaxL + L - 1];
+            for (int k = lane; k < L; k += 32) {
+              float d = last - row[kMaxL + k];
+              if (a.clamp_decay) d = fminf(d, 0.0f);
+              sc[hd * kMaxL + k] = fast_exp(d) * row[k];
             }
-            if (ok) mma_commit(bar_empty(s));
-            PROF_ADD(3, PROF_T() - tn2);
           }
-          if (ok) mma_commit(bar_acc_full(buf));
-        }
-      }
-#ifdef SSD_EXP_PROF
-      prof[7] = clock64() - tstart;
-      for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 8 + i] = prof[i];
-#endif
-    }
-  } else {
-    // ============================== scale vectors =====================================
-    // Two warps turn each chunk's dt / dA_cumsum rows into the per-position factors
-    // exp(min(a_last - a_k, 0)) * dt_k, one item ahead of the B-scaling warps.
-    const int vt = tid - (C::EPI_WARPS + 2) * 32;
-    uint32_t item = 0;
-    bool ok = true;
-    for (int j = 0; j < rg.m && ok; ++j) {
-      int strip, c0, c1;
-      get_segment(rg, nchunks, j, strip, c0, c1);
-      for (int c = c0; c < c1 && ok; ++c, ++item) {
-        const int r = item % C::ND;
-        ok = mbar_wait(bar_dd_full(r), (item / C::ND) & 1, wc, kWaitDdFull);
-        if (!ok) break;
-        if (item >= 2) {
-          ok = mbar_wait(bar_sc_free(item & 1), ((item >> 1) - 1) & 1, wc, kWaitGroup);
-          if (!ok) break;
-        }
-        const float* dd = reinterpret_cast<const float*>(smem + C::OFF_DTDA + r * C::DTDA_SLOT);
-        float* sc = reinterpret_cast<float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
-#pragma unroll
-        for (int hd = 0; hd < HPC; ++hd) {
-          const float* row = dd + hd * 2 * kMaxL;
-          const float last = row[kMaxL + L - 1];
-          for (int k = vt; k < L; k += C::SCV_THREADS) {
-            float d = last - row[kMaxL + k];
-            if (a.clamp_decay) d = fminf(d, 0.0f);
-            sc[hd * kMaxL + k] = fast_exp(d) * row[k];
+          __syncwarp();                       // every lane has read the rows and written its factors
+          if (lane == 0) {
+            mbar_arrive(bar_sc_ready(item & 1));
+            fence_proxy_async_smem();         // the rows were read; the slot is refilled by bulk copies
+            if (pre_valid()) load_rows(pstrip, pc, r);
           }
-        }
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar_sc_ready(item & 1));
-          mbar_arrive(bar_dd_empty(r));
+          pre_next();
         }
       }
     }
-  }
   } else if (warp >= C::SCALE_WARP0) {
     // ============================== B scaling =========================================
     if constexpr (C::REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REGS_SCALE));
-    const int stid = tid - C::SCALE_WARP0 * 32;
+    // Warp (qn, kh): TMEM lane quadrant qn = dstate columns 32 qn .. 32 qn + 31, and positions
+    // 32 kh .. 32 kh + 31 of every 64-position stage.  For each block of 16 dstate columns two
+    // ldmatrix.trans bring the raw 16-bit B values as (k, k + 1) pairs per column, which is the
+    // arrangement tcgen05.st (16x128b) wants for an A operand with the dstate index on the
+    // lanes; each pair is widened, multiplied by its positions' factors in fp32, rounded back
+    // to the input type (the reference's rounding point) and stored to the head's A slot.
+    const int sw = warp - C::SCALE_WARP0;
+    const int qn = sw & 3, kh = sw >> 2;
+    const int lm = lane >> 3, lr = lane & 7;              // ldmatrix: matrix and row this lane addresses
+    // raw B tile: two boxes of 64 columns; a row (position) is 128 bytes, its 16-byte pieces
+    // swizzled by the row index modulo 8, which here is lr
+    const uint32_t ld_base = (uint32_t)((qn >> 1) * (C::RAWB_BYTES / 2) + (kh * 32 + (lm >> 1) * 8 + lr) * 128);
+    const uint32_t ld_piece[2] = {(uint32_t)((((qn & 1) * 4 + (lm & 1)) ^ lr) << 4),
+                                  (uint32_t)((((qn & 1) * 4 + 2 + (lm & 1)) ^ lr) << 4)};
+    const uint32_t st_lane = static_cast<uint32_t>(qn * 32) << 16;
+    const int sq = 2 * (lane & 3);                        // first of this lane's two positions in a block of 8
     uint32_t it = 0, item = 0;
     bool ok = true;
 #ifdef SSD_EXP_PROF
@@ -470,65 +475,60 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         long long ts1 = PROF_T();
         PROF_ADD(0, ts1 - ts0);
         const float* sc = reinterpret_cast<const float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
-        PROF_ADD(1, PROF_T() - ts1);
         const int limit = min(L, a.seqlen - c * L);
         const int ksteps = (limit + kKT - 1) / kKT;
         for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
           const int s = it % C::NS;
+          const int sa = it % C::NA;
           long long tu0 = PROF_T();
           ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
           if (!ok) break;
+          ok = mbar_wait(bar_a_free(sa), ((it / C::NA) & 1) ^ 1, wc, kWaitBsEmpty);
+          if (!ok) break;
+          tc_fence_after();
           long long tu1 = PROF_T();
           PROF_ADD(2, tu1 - tu0);
-          const uint8_t* raw = smem + C::OFF_STAGES + s * C::STAGE_BYTES;
-          uint8_t* dst = smem + C::OFF_STAGES + s * C::STAGE_BYTES;
-          const float* sch = sc + ks * kKT;
-          // One pass over the raw B tile produces the scaled tile of every head of the CTA.
-          // All loads of a thread are issued before the first use, so the shared-memory
-          // latency is paid once per stage rather than once per 16 bytes.
-          constexpr int kChunks = C::RAWB_BYTES / 16;
-          constexpr int kPerThread = (kChunks + C::SCALE_THREADS - 1) / C::SCALE_THREADS;
-          const int vt = stid;
-          uint4 v[kPerThread];
 #ifndef SSD_EXP_NOSCALE
+          const uint32_t raw = sbase + C::OFF_STAGES + s * C::STAGE_BYTES + ld_base;
+          // factors of this lane's positions: block i of 8 positions -> (f[k], f[k + 1])
+          float2 f[HPC][4];
 #pragma unroll
-          for (int q = 0; q < kPerThread; ++q) {
-            const int i = vt + q * C::SCALE_THREADS;
-            if (kChunks % C::SCALE_THREADS == 0 || i < kChunks)
-              v[q] = *reinterpret_cast<const uint4*>(raw + i * 16);
-          }
+          for (int hd = 0; hd < HPC; ++hd)
 #pragma unroll
-          for (int q = 0; q < kPerThread; ++q) {
-            const int i = vt + q * C::SCALE_THREADS;
-            if (kChunks % C::SCALE_THREADS == 0 || i < kChunks) {
-              const int off = i * 16;
-              const int row = (off & (C::RAWB_BYTES / 2 - 1)) >> 7;      // k within the stage
-              float2 e0, e1, e2, e3;
-              Pack<T>::unpack(v[q].x, e0.x, e0.y);
-              Pack<T>::unpack(v[q].y, e1.x, e1.y);
-              Pack<T>::unpack(v[q].z, e2.x, e2.y);
-              Pack<T>::unpack(v[q].w, e3.x, e3.y);
+            for (int i = 0; i < 4; ++i)
+              f[hd][i] = *reinterpret_cast<const float2*>(sc + hd * kMaxL + ks * kKT + kh * 32 + i * 8 + sq);
 #pragma unroll
-              for (int hd = 0; hd < HPC; ++hd) {
-                const float f = sch[hd * kMaxL + row];
-                const float2 ff = make_float2(f, f);
-                const float2 r0 = __fmul2_rn(e0, ff), r1 = __fmul2_rn(e1, ff);
-                const float2 r2 = __fmul2_rn(e2, ff), r3 = __fmul2_rn(e3, ff);
-                uint4 o;
-                o.x = Pack<T>::pack(r0.x, r0.y);
-                o.y = Pack<T>::pack(r1.x, r1.y);
-                o.z = Pack<T>::pack(r2.x, r2.y);
-                o.w = Pack<T>::pack(r3.x, r3.y);
-                *reinterpret_cast<uint4*>(dst + C::a_tile_off(hd) + off) = o;
+          for (int nbk = 0; nbk < 2; ++nbk) {               // dstate columns 16 nbk .. of the quadrant
+            uint32_t r[8];
+            {
+              uint32_t t4[4];
+              ldmatrix_x4_trans(raw + ld_piece[nbk], t4);              // positions 0..15 of the half
+              r[0] = t4[0]; r[1] = t4[1]; r[2] = t4[2]; r[3] = t4[3];
+              ldmatrix_x4_trans(raw + 16 * 128 + ld_piece[nbk], t4);   // positions 16..31
+              r[4] = t4[0]; r[5] = t4[1]; r[6] = t4[2]; r[7] = t4[3];
+            }
+            float2 e[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) Pack<T>::unpack(r[i], e[i].x, e[i].y);
+#pragma unroll
+            for (int hd = 0; hd < HPC; ++hd) {
+              uint32_t o[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float2 v = __fmul2_rn(e[i], f[hd][i >> 1]);
+                o[i] = Pack<T>::pack(v.x, v.y);
               }
+              tmem_st_16x128b_x4(tmem_base + st_lane + (static_cast<uint32_t>(nbk * 16) << 16) + C::TMEM_A0 +
+                                     (hd * C::NA + sa) * C::A_COLS + kh * 16, o);
             }
           }
+          tmem_st_wait();
 #endif
           long long tu2 = PROF_T();
           PROF_ADD(3, tu2 - tu1);
-          fence_proxy_async_smem();
+          tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_bs_full(s));
+          if (lane == 0) mbar_arrive(bar_bs_full(sa));
           PROF_ADD(4, PROF_T() - tu2);
         }
         // (the __syncwarp of the last stage ordered every lane's reads of the scale vector)
@@ -536,7 +536,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       }
     }
 #ifdef SSD_EXP_PROF
-    if (stid == 0) {
+    if (sw == 0 && lane == 0) {
       prof[7] = clock64() - tstart;
       for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 16 + i] = prof[i];
     }
@@ -650,7 +650,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         if (a.mode == 0)
           decay = fast_exp(__ldg(a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2] + (L - 1)));
         long long te0 = PROF_T();
-        ok = mbar_wait(bar_acc_full(buf), (item / C::NBUF) & 1, wc, kWaitAccFull, 128);
+        ok = mbar_wait(bar_acc_full(hd, buf), (item / C::NBUF) & 1, wc, kWaitAccFull, 128);
         if (!ok) break;
         long long te1 = PROF_T();
         PROF_ADD(0, te1 - te0);
