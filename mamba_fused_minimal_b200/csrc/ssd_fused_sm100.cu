@@ -55,10 +55,17 @@ enum WaitCode {
 
 template <int HPC>
 struct Cfg {
-  static constexpr int NS = 6;                        // shared-memory stages (raw B tile + x tiles)
-  static constexpr int NA = 2;                        // scaled-B (A operand) slots per head in TMEM
+#ifndef SSD_NS
+#define SSD_NS 6
+#endif
+  static constexpr int NS = SSD_NS;                   // shared-memory stages (raw B tile + x tiles)
+#ifndef SSD_NA
+#define SSD_NA 2
+#define SSD_NBUF2 3
+#endif
+  static constexpr int NA = SSD_NA;                   // scaled-B (A operand) slots per head in TMEM
   static constexpr int ND = 2;                        // dt/dA row slots
-  static constexpr int NBUF = (HPC == 2) ? 3 : 4;     // TMEM accumulators per head
+  static constexpr int NBUF = (HPC == 2) ? SSD_NBUF2 : 4;     // TMEM accumulators per head
   static constexpr int EPI_WARPS = 4 * HPC;
   // B-scaling warps: a warp can only write the TMEM lanes of its quadrant (warp index % 4), so
   // four quadrants x two halves of a stage's 64 positions
@@ -93,8 +100,7 @@ struct Cfg {
   static constexpr int B_FULL = 0;                       // [NS]  stage loaded (TMA bytes)
   static constexpr int B_EMPTY = B_FULL + NS;            // [NS]  stage consumed (one commit per MMA issuer)
   static constexpr int B_BS = B_EMPTY + NS;              // [NA]  scaled B written (one arrival per scaling warp)
-  static constexpr int B_AFREE = B_BS + NA;              // [NA]  scaled B consumed (one commit per MMA issuer)
-  static constexpr int B_DD = B_AFREE + NA;              // [ND]  dt / dA rows loaded
+  static constexpr int B_DD = B_BS + NA;                 // [ND]  dt / dA rows loaded
   static constexpr int B_ACCF = B_DD + ND;               // [HPC][NBUF] accumulator complete
   static constexpr int B_ACCE = B_ACCF + HPC * NBUF;     // [HPC][NBUF] accumulator drained (4 epilogue warps)
   static constexpr int B_SCR = B_ACCE + HPC * NBUF;      // [2]   scale vector ready
@@ -108,21 +114,19 @@ struct Cfg {
   static constexpr int OFF_STAGING = (OFF_CTL + 64 + 1023) / 1024 * 1024;
   static constexpr int SMEM_BYTES = OFF_STAGING + EPI_WARPS * STAGING_BYTES + 1024;   // + alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-  // Register budget per role (setmaxnreg), used where the CTA has more than 512 threads and
-  // would otherwise be held to the launch allocation of LAUNCH_REGS per thread, too few for the
-  // epilogue's 64 state values.  setmaxnreg.inc waits for registers that other roles give back,
-  // so the per-role counts must fit in what the CTA is launched with, or the wait never ends.
-#ifndef SSD_REGS_EPI
-#define SSD_REGS_EPI 136
-#define SSD_REGS_SCALE 80
-#define SSD_REGS_SERVICE 40
-#endif
-  static constexpr bool REBALANCE = WARPS * 32 > 512;
+  // Register budget per role (setmaxnreg).  The CTA is launched with LAUNCH_REGS per thread,
+  // too few for the epilogue's 64 state values at 640 threads; the scaling and service warps
+  // give registers back and the epilogue warps take them.  setmaxnreg.inc waits for registers
+  // that other roles release, so the per-role counts must fit in what the CTA is launched
+  // with, or the wait never ends.
   static constexpr int LAUNCH_REGS = 65536 / (WARPS * 32) / 8 * 8;
-  static constexpr int REGS_EPI = SSD_REGS_EPI, REGS_SCALE = SSD_REGS_SCALE, REGS_SERVICE = SSD_REGS_SERVICE;
-  static_assert(!REBALANCE || (EPI_WARPS * REGS_EPI + SERVICE_WARPS * REGS_SERVICE + SCALE_WARPS * REGS_SCALE) <=
-                                  WARPS * LAUNCH_REGS, "per-role register counts exceed the launch allocation");
-  static_assert(!REBALANCE || (REGS_SCALE <= LAUNCH_REGS && REGS_SERVICE <= LAUNCH_REGS && REGS_EPI >= LAUNCH_REGS),
+  static constexpr int REGS_EPI = (HPC == 2) ? 144 : 168;
+  static constexpr int REGS_SCALE = (HPC == 2) ? 72 : 96;
+  static constexpr int REGS_SERVICE = 40;
+  static constexpr bool REBALANCE = true;
+  static_assert(EPI_WARPS * REGS_EPI + SERVICE_WARPS * REGS_SERVICE + SCALE_WARPS * REGS_SCALE <= WARPS * LAUNCH_REGS,
+                "per-role register counts exceed the launch allocation");
+  static_assert(REGS_SCALE <= LAUNCH_REGS && REGS_SERVICE <= LAUNCH_REGS && REGS_EPI >= LAUNCH_REGS,
                 "scaling and service roles give registers back, the epilogue takes them");
 };
 
@@ -231,7 +235,6 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   auto bar_full = [&](int s) { return bars + 8u * (C::B_FULL + s); };
   auto bar_empty = [&](int s) { return bars + 8u * (C::B_EMPTY + s); };
   auto bar_bs_full = [&](int t) { return bars + 8u * (C::B_BS + t); };
-  auto bar_a_free = [&](int t) { return bars + 8u * (C::B_AFREE + t); };
   auto bar_dd_full = [&](int r) { return bars + 8u * (C::B_DD + r); };
   auto bar_acc_full = [&](int hd, int b) { return bars + 8u * (C::B_ACCF + hd * C::NBUF + b); };
   auto bar_acc_empty = [&](int hd, int b) { return bars + 8u * (C::B_ACCE + hd * C::NBUF + b); };
@@ -244,7 +247,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
 
   if (tid == 0) {
     for (int s = 0; s < C::NS; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), HPC); }
-    for (int t = 0; t < C::NA; ++t) { mbar_init(bar_bs_full(t), C::SCALE_WARPS); mbar_init(bar_a_free(t), HPC); }
+    for (int t = 0; t < C::NA; ++t) mbar_init(bar_bs_full(t), C::SCALE_WARPS);
     for (int r = 0; r < C::ND; ++r) mbar_init(bar_dd_full(r), 1);
     for (int hd = 0; hd < HPC; ++hd)
       for (int b = 0; b < C::NBUF; ++b) { mbar_init(bar_acc_full(hd, b), 1); mbar_init(bar_acc_empty(hd, b), 4); }
@@ -300,11 +303,15 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
               const int s = it % C::NS;
               ok = mbar_wait(bar_empty(s), ((it / C::NS) & 1) ^ 1, wc, kWaitStageEmpty);
               if (!ok) break;
-              mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
               const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
               const int l0 = c * L + ks * kKT;
+#ifdef SSD_EXP_NOBLOAD
+              mbar_expect_tx(bar_full(s), C::LOAD_BYTES - C::RAWB_BYTES);
+#else
+              mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
               tma_load_4d_hint(st, &tmap_B, bar_full(s), 0, g, l0, b, keep);
               tma_load_4d_hint(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b, keep);
+#endif
 #pragma unroll
               for (int hd = 0; hd < HPC; ++hd)
                 tma_load_4d_hint(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b, stream_once);
@@ -362,7 +369,6 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
 #pragma unroll
               for (int k16 = 0; k16 < kKT / 16; ++k16)
                 mma_f16_ts(d_tmem, a_tmem + k16 * 8, bd_s + (uint64_t)((k16 * 2048) >> 4), idesc, (ks | k16) != 0 ? 1u : 0u);
-              mma_commit(bar_a_free(sa));
               mma_commit(bar_empty(s));
               PROF_ADD(3, PROF_T() - tn2);
             }
@@ -483,8 +489,13 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           long long tu0 = PROF_T();
           ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
           if (!ok) break;
-          ok = mbar_wait(bar_a_free(sa), ((it / C::NA) & 1) ^ 1, wc, kWaitBsEmpty);
-          if (!ok) break;
+          // the A slot is free once the MMAs of iteration it - NA are complete, which is what
+          // releases that iteration's stage
+          if (it >= (uint32_t)C::NA) {
+            const uint32_t pit = it - C::NA;
+            ok = mbar_wait(bar_empty(pit % C::NS), (pit / C::NS) & 1, wc, kWaitBsEmpty);
+            if (!ok) break;
+          }
           tc_fence_after();
           long long tu1 = PROF_T();
           PROF_ADD(2, tu1 - tu0);
