@@ -42,8 +42,8 @@ WORKLOAD = dict(name="mamba2-2.7b-layer", batch=8, seqlen=4096, nheads=80, headd
                 chunk_size=256)
 FALLBACK_HBM_GBS = 6650.0
 # DRAM traffic of the fused kernel per token, from the ncu capture summarised in
-# profiles/fused_state_kernel_mamba2-2.7b_batch4.md: (183.0 MB + 94.4 MB) / 16384 tokens
-NCU_TRAFFIC_PER_TOKEN = (183.02e6 + 94.4e6) / 16384
+# profiles/fused_state_kernel_mamba2-2.7b_batch4.md: (182.8 MB + 94.4 MB) / 16384 tokens
+NCU_TRAFFIC_PER_TOKEN = (182.75e6 + 94.4e6) / 16384
 
 
 def algorithmic_bytes(w, in_bytes=2, out_bytes=2, with_cumsum=True):
@@ -407,8 +407,8 @@ def main():
                            path_bytes_per_step=algorithmic_bytes(w, with_cumsum=True)),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_PER_TOKEN * tokens_per_rank,
-                         "traffic_source": "ncu dram__bytes_read+write of a batch-4 capture (183.0 MB read; writes "
-                                           "counted as the 94.4 MB the launch must write, 64.9 MB of it reached DRAM "
+                         "traffic_source": "ncu dram__bytes_read+write of a batch-4 capture (182.8 MB read; writes "
+                                           "counted as the 94.4 MB the launch must write, 52.1 MB of it reached DRAM "
                                            "before the kernel ended), scaled by tokens",
                          "peak_kind": peak_kind,
                          "kernel": "fused_state_kernel", "bytes_per_launch": fused_bytes,

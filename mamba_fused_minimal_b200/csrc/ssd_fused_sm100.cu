@@ -14,21 +14,27 @@
 // Per chunk and head: states^T[n, p] = sum_k Bs[k, n] * x[k, p] with
 // Bs = cast_in(B * exp(min(dA_last - dA_k, 0)) * dt_k)   (the reference's rounding point,
 // kernels/ssd_chunk_state.py:153-159), a 128 x 64 x L contraction done by tcgen05.mma with
-// the accumulator in TMEM (lanes = dstate index n, columns = headdim index p).
+// both the A operand (Bs, dstate on the lanes) and the accumulator (lanes = dstate index n,
+// columns = headdim index p) in tensor memory; only x is an operand from shared memory.
 //
-// Warp roles (HPC = heads per CTA sharing one B tile):
-//   warps [0, 4*HPC)      epilogue: one warpgroup per head; tcgen05.ld the chunk state,
-//                         S <- exp(dA_last) * S + state in registers, store out / final
+// Warp roles (HPC = heads per CTA sharing one B tile), in warpgroups so that each role can be
+// given its own register budget (setmaxnreg):
+//   warps [0, 4*HPC)      epilogue, one warpgroup per head: tcgen05.ld the chunk state in the
+//                         matrix-fragment arrangement, S <- exp(dA_last) * S + state in
+//                         registers; 16-bit passed states go out through stmatrix + one TMA
+//                         store per warp and 32 rows, everything else with plain stores
 //   warp  4*HPC           TMA producer: per 64-position stage the raw B tile and one x tile per
-//                         head; per chunk the dt / dA_cumsum rows (bulk copy)
-//   warp  4*HPC + 1       MMA issuer (one thread), TMEM allocation
-//   remaining warps       scale B by the per-position decay*dt in fp32, round to the input
-//                         type: the last head's A operand overwrites the raw tile in place,
-//                         the other heads' go to the stage's spare tiles (a thread reads its
-//                         16-byte pieces into registers before it writes any), then
-//                         generic -> async proxy fence and one mbarrier arrival per warp.
-// One ring of stages carries a tile through TMA -> scaling -> MMA, so the latency of each
-// handoff is covered by the ring depth instead of needing a second ring of scaled tiles.
+//                         head into a ring of six stages
+//   warps 4*HPC + 1, + 2  MMA issuers, one thread per head (the first also owns the TMEM
+//                         allocation); A from tensor memory, four K = 16 steps per stage
+//   warp  4*HPC + 3       loads each chunk's dt / dA_cumsum rows (bulk copies) and turns them
+//                         into the per-position factors exp(min(a_last - a_k, 0)) * dt_k
+//   8 further warps       B scaling: ldmatrix.trans brings the raw 16-bit B values as (k, k+1)
+//                         pairs per dstate column, they are widened, multiplied by their
+//                         positions' factors in fp32, rounded back to the input type and
+//                         written with tcgen05.st to the head's A slot in tensor memory
+// The accumulator of a chunk is complete after its last stage; up to NBUF chunks of MMAs run
+// ahead of the epilogue.
 #include <cuda.h>
 
 #include <mutex>
@@ -55,17 +61,10 @@ enum WaitCode {
 
 template <int HPC>
 struct Cfg {
-#ifndef SSD_NS
-#define SSD_NS 6
-#endif
-  static constexpr int NS = SSD_NS;                   // shared-memory stages (raw B tile + x tiles)
-#ifndef SSD_NA
-#define SSD_NA 2
-#define SSD_NBUF2 3
-#endif
-  static constexpr int NA = SSD_NA;                   // scaled-B (A operand) slots per head in TMEM
+  static constexpr int NS = 6;                        // shared-memory stages (raw B tile + x tiles)
+  static constexpr int NA = 2;                        // scaled-B (A operand) slots per head in TMEM
   static constexpr int ND = 2;                        // dt/dA row slots
-  static constexpr int NBUF = (HPC == 2) ? SSD_NBUF2 : 4;     // TMEM accumulators per head
+  static constexpr int NBUF = (HPC == 2) ? 3 : 4;     // TMEM accumulators per head
   static constexpr int EPI_WARPS = 4 * HPC;
   // B-scaling warps: a warp can only write the TMEM lanes of its quadrant (warp index % 4), so
   // four quadrants x two halves of a stage's 64 positions
@@ -76,7 +75,6 @@ struct Cfg {
   static constexpr int SCALE_WARP0 = EPI_WARPS + SERVICE_WARPS;
   static constexpr int WARPS = SCALE_WARP0 + SCALE_WARPS;
   static constexpr int THREADS = WARPS * 32;
-  static constexpr int SCALE_THREADS = SCALE_WARPS * 32;
   static constexpr int RAWB_BYTES = kKT * kN * 2;     // 16 KiB: two 64-column SW128 boxes
   static constexpr int X_BYTES = kKT * kP * 2;        // 8 KiB: one SW128 box
   // a stage: the raw B tile, then one x tile per head
@@ -151,14 +149,6 @@ struct FusedArgs {
                           // carried state is added afterwards by segment_fixup_kernel
 };
 
-#ifdef SSD_EXP_PROF
-__device__ long long g_prof[160 * 32];
-#define PROF_T() clock64()
-#define PROF_ADD(i, v) prof[(i)] += (v)
-#else
-#define PROF_T() 0ll
-#define PROF_ADD(i, v)
-#endif
 
 struct Range {
   long long lo, hi;
@@ -305,13 +295,9 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
               if (!ok) break;
               const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
               const int l0 = c * L + ks * kKT;
-#ifdef SSD_EXP_NOBLOAD
-              mbar_expect_tx(bar_full(s), C::LOAD_BYTES - C::RAWB_BYTES);
-#else
               mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
               tma_load_4d_hint(st, &tmap_B, bar_full(s), 0, g, l0, b, keep);
               tma_load_4d_hint(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b, keep);
-#endif
 #pragma unroll
               for (int hd = 0; hd < HPC; ++hd)
                 tma_load_4d_hint(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b, stream_once);
@@ -334,19 +320,13 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         const uint64_t bdesc0 = smem_desc_sw128(sbase + C::OFF_STAGES + C::OFF_XT + mhd * C::X_BYTES, C::X_BYTES, 1024);
         uint32_t it = 0, item = 0;
         bool ok = true;
-#ifdef SSD_EXP_PROF
-        long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        const long long tstart = clock64();
-#endif
         for (int j = 0; j < rg.m && ok; ++j) {
           int strip, c0, c1;
           get_segment(rg, nchunks, j, strip, c0, c1);
           for (int c = c0; c < c1 && ok; ++c, ++item) {
             const int buf = item % C::NBUF;
-            long long tm0 = PROF_T();
             ok = mbar_wait(bar_acc_empty(mhd, buf), ((item / C::NBUF) & 1) ^ 1, wc, kWaitAccEmpty);
             if (!ok) break;
-            PROF_ADD(0, PROF_T() - tm0);
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (mhd * C::NBUF + buf) * kP;
             const int limit = min(L, a.seqlen - c * L);
@@ -354,15 +334,10 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
               const int s = it % C::NS;
               const int sa = it % C::NA;
-              long long tn0 = PROF_T();
               ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
               if (!ok) break;
-              long long tn1 = PROF_T();
-              PROF_ADD(1, tn1 - tn0);
               ok = mbar_wait(bar_bs_full(sa), (it / C::NA) & 1, wc, kWaitBsFull);
               if (!ok) break;
-              long long tn2 = PROF_T();
-              PROF_ADD(2, tn2 - tn1);
               tc_fence_after();
               const uint64_t bd_s = bdesc0 + (uint64_t)((s * C::STAGE_BYTES) >> 4);
               const uint32_t a_tmem = tmem_base + C::TMEM_A0 + (mhd * C::NA + sa) * C::A_COLS;
@@ -370,17 +345,10 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
               for (int k16 = 0; k16 < kKT / 16; ++k16)
                 mma_f16_ts(d_tmem, a_tmem + k16 * 8, bd_s + (uint64_t)((k16 * 2048) >> 4), idesc, (ks | k16) != 0 ? 1u : 0u);
               mma_commit(bar_empty(s));
-              PROF_ADD(3, PROF_T() - tn2);
             }
             if (ok) mma_commit(bar_acc_full(mhd, buf));
           }
         }
-#ifdef SSD_EXP_PROF
-        if (mhd == 0) {
-          prof[7] = clock64() - tstart;
-          for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 8 + i] = prof[i];
-        }
-#endif
       }
     } else if (warp == C::EPI_WARPS + 3) {
       // ============================== scale vectors ===================================
@@ -467,26 +435,18 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     const int sq = 2 * (lane & 3);                        // first of this lane's two positions in a block of 8
     uint32_t it = 0, item = 0;
     bool ok = true;
-#ifdef SSD_EXP_PROF
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long tstart = clock64();
-#endif
     for (int j = 0; j < rg.m && ok; ++j) {
       int strip, c0, c1;
       get_segment(rg, nchunks, j, strip, c0, c1);
       for (int c = c0; c < c1 && ok; ++c, ++item) {
-        long long ts0 = PROF_T();
         ok = mbar_wait(bar_sc_ready(item & 1), (item >> 1) & 1, wc, kWaitDdFull);
         if (!ok) break;
-        long long ts1 = PROF_T();
-        PROF_ADD(0, ts1 - ts0);
         const float* sc = reinterpret_cast<const float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
         const int limit = min(L, a.seqlen - c * L);
         const int ksteps = (limit + kKT - 1) / kKT;
         for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
           const int s = it % C::NS;
           const int sa = it % C::NA;
-          long long tu0 = PROF_T();
           ok = mbar_wait(bar_full(s), (it / C::NS) & 1, wc, kWaitStageFull);
           if (!ok) break;
           // the A slot is free once the MMAs of iteration it - NA are complete, which is what
@@ -497,9 +457,6 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             if (!ok) break;
           }
           tc_fence_after();
-          long long tu1 = PROF_T();
-          PROF_ADD(2, tu1 - tu0);
-#ifndef SSD_EXP_NOSCALE
           const uint32_t raw = sbase + C::OFF_STAGES + s * C::STAGE_BYTES + ld_base;
           // factors of this lane's positions: block i of 8 positions -> (f[k], f[k + 1])
           float2 f[HPC][4];
@@ -534,24 +491,14 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             }
           }
           tmem_st_wait();
-#endif
-          long long tu2 = PROF_T();
-          PROF_ADD(3, tu2 - tu1);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_bs_full(sa));
-          PROF_ADD(4, PROF_T() - tu2);
         }
         // (the __syncwarp of the last stage ordered every lane's reads of the scale vector)
         if (ok && lane == 0) mbar_arrive(bar_sc_free(item & 1));
       }
     }
-#ifdef SSD_EXP_PROF
-    if (sw == 0 && lane == 0) {
-      prof[7] = clock64() - tstart;
-      for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 16 + i] = prof[i];
-    }
-#endif
   } else {
     // ============================== epilogue ==========================================
     if constexpr (C::REBALANCE) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::REGS_EPI));
@@ -581,10 +528,6 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     float S[kP];
     uint32_t item = 0, epi_syncs = 0;
     bool ok = true;
-#ifdef SSD_EXP_PROF
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long tstart = clock64();
-#endif
     // Stores 32 rows (p = 32 hq ..) of a (kP x kN) tile whose element (0, 0) is at element
     // offset `tile` of `base`, row pitch `pitch`, from the fragment values vals[0..31].
     // `map` != nullptr: 16-bit tile (b = cb, chunk = cc, head = ch) of the tensor behind the map.
@@ -622,9 +565,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-#ifndef SSD_EXP_NOSTORE
         tma_store_5d(map, stg, wq * 32, hq * 32, ch, cc, cb);
-#endif
         bulk_commit();
       }
     };
@@ -660,11 +601,8 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         float decay = 0.0f;
         if (a.mode == 0)
           decay = fast_exp(__ldg(a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2] + (L - 1)));
-        long long te0 = PROF_T();
         ok = mbar_wait(bar_acc_full(hd, buf), (item / C::NBUF) & 1, wc, kWaitAccFull, 128);
         if (!ok) break;
-        long long te1 = PROF_T();
-        PROF_ADD(0, te1 - te0);
         tc_fence_after();
         const uint32_t taddr = tmem_base + lane_sel + (hd * C::NBUF + buf) * kP;
 #pragma unroll
@@ -699,7 +637,6 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             for (int i = 0; i < 32; ++i) S[hq * 32 + i] = fmaf(decay, cur[i], v[i]);
           }
         }
-        PROF_ADD(1, PROF_T() - te1);
       }
       if (!ok || a.mode != 0) continue;
       if (c1 == nchunks) {
@@ -720,12 +657,6 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       }
     }
     bulk_wait_all();            // this thread's bulk copies are complete before the CTA retires
-#ifdef SSD_EXP_PROF
-    if (tid == 0) {
-      prof[7] = clock64() - tstart;
-      for (int i = 0; i < 8; ++i) g_prof[blockIdx.x * 32 + 24 + i] = prof[i];
-    }
-#endif
   }
 
   // ================================ teardown ==========================================
@@ -956,7 +887,6 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   a.mode = mode;
 
   const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
-  const long long strips = (long long)a.batch * a.strips_per_batch;
   int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
   auto kern = (p.out_dtype == SSD_F32 && mode == 0) ? fused_state_kernel<T, HPC, true> : fused_state_kernel<T, HPC, false>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -995,11 +925,6 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
 
 }  // namespace
 
-#ifdef SSD_EXP_PROF
-extern "C" __attribute__((visibility("default"))) int ssd_debug_read_prof(long long* dst, int n) {
-  return (int)cudaMemcpyFromSymbol(dst, g_prof, sizeof(long long) * n);
-}
-#endif
 
 int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why) {
   const ssd_state_inputs_t& in = p.in;
