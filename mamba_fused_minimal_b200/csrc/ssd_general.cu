@@ -17,49 +17,133 @@ namespace ssd {
 // =====================================================================================
 constexpr int CS_HT = 16;        // heads per block
 constexpr int CS_THREADS = 256;
+constexpr int CS_PER = 8;        // consecutive positions per lane in the scan
+constexpr int CS_ROUND = 32 * CS_PER;
+
+// 16 bytes of consecutive heads of one position, widened to fp32.
+template <typename DT> struct DtVec;
+template <> struct DtVec<float> {
+  static constexpr int VEC = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+};
+template <> struct DtVec<__nv_bfloat16> {
+  static constexpr int VEC = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+template <> struct DtVec<__half> {
+  static constexpr int VEC = 8;
+  static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+};
 
 // Block (head tile, chunk, batch).  Phase 1 reads the (L x CS_HT) tile of dt with heads
 // fastest (the input's contiguous dimension), applies bias / softplus / clamp / tail mask
-// and parks dt' in shared memory.  Phase 2: one warp per head walks the chunk in blocks of
-// 32 positions, doing a shuffle scan of dt'*A with a running carry, and writes both outputs
-// with positions fastest (the outputs' contiguous dimension).
+// and parks dt' in shared memory, one row per head.  FAST: the heads of a position are
+// contiguous and 16-byte aligned, a thread takes 16 bytes of them per load; otherwise any
+// strides and dtype, one element per load.  Phase 2: one warp per head; a lane takes
+// CS_PER consecutive positions (two 16-byte reads), scans them serially, the lane totals go
+// through one shuffle scan, and both outputs are written with positions fastest (the
+// outputs' contiguous dimension), 32 bytes per lane and tensor.
+template <typename DT, bool FAST>
 __global__ void __launch_bounds__(CS_THREADS)
-chunk_cumsum_kernel(ssd_chunk_cumsum_params_t p, int nchunks) {
-  extern __shared__ float tile[];                       // [L][CS_HT + 1]
+chunk_cumsum_kernel(ssd_chunk_cumsum_params_t p, int nchunks, int pitch, int vec) {
+  extern __shared__ __align__(16) float tile[];         // [CS_HT][pitch], pitch % 4 == 0
   const int h0 = blockIdx.x * CS_HT;
   const int c = blockIdx.y;
   const int b = blockIdx.z;
   const int L = p.chunk_size;
   const int limit = min(L, p.seqlen - c * L);
+  const int Lr = (L + CS_ROUND - 1) / CS_ROUND * CS_ROUND;
   const int tid = threadIdx.x;
 
-  // a thread always serves the same head (CS_THREADS is a multiple of CS_HT)
-  const int hh_t = tid % CS_HT;
-  const int h_t = h0 + hh_t;
-  const bool head_ok = h_t < p.nheads;
-  const float bias = (head_ok && p.dt_bias != nullptr)
-                         ? load_f(p.dt_bias, p.bias_dtype, (int64_t)h_t * p.bias_stride) : 0.0f;
-  const int64_t dt_base = (int64_t)b * p.dt_stride_b + (int64_t)c * L * p.dt_stride_l + (int64_t)h_t * p.dt_stride_h;
-  constexpr int kRowsPerPass = CS_THREADS / CS_HT;     // 16 positions per pass
-  constexpr int kUnroll = 8;                           // loads in flight per thread
-  for (int k0 = tid / CS_HT; k0 < L; k0 += kRowsPerPass * kUnroll) {
-    float v[kUnroll];
+  if constexpr (FAST) {
+    constexpr int VEC = DtVec<DT>::VEC;
+    constexpr int TPP = CS_HT / VEC;                   // threads per position
+    constexpr int PPP = CS_THREADS / TPP;              // positions per pass
+    const int sub = tid % TPP, kk = tid / TPP;
+    float bias[VEC];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int k = k0 + u * kRowsPerPass;
-      v[u] = (head_ok && k < limit) ? load_f(p.dt, p.dt_dtype, dt_base + (int64_t)k * p.dt_stride_l) : 0.0f;
-    }
+    for (int j = 0; j < VEC; ++j)
+      bias[j] = p.dt_bias != nullptr ? load_f(p.dt_bias, p.bias_dtype, (int64_t)(h0 + sub * VEC + j) * p.bias_stride) : 0.0f;
+    const DT* src = static_cast<const DT*>(p.dt) + (int64_t)b * p.dt_stride_b + (int64_t)c * L * p.dt_stride_l + h0 + sub * VEC;
+    float* dst = tile + sub * VEC * pitch;
+    const bool sp = p.dt_softplus != 0;
+    const float lo = p.dt_min, hi = p.dt_max;
+    for (int k0 = kk; k0 < Lr; k0 += PPP * 2) {
+      float v[2][VEC];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int k = k0 + u * kRowsPerPass;
-      if (k < L) {
-        float t = 0.0f;
-        if (head_ok && k < limit) {
-          t = v[u] + bias;
-          if (p.dt_softplus) t = softplus_ref(t);
-          t = fminf(fmaxf(t, p.dt_min), p.dt_max);
+      for (int u = 0; u < 2; ++u) {
+        const int k = k0 + u * PPP;
+        if (k < limit) {
+          DtVec<DT>::load(src + (int64_t)k * p.dt_stride_l, v[u]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) v[u][j] = 0.0f;
         }
-        tile[k * (CS_HT + 1) + hh_t] = t;
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int k = k0 + u * PPP;
+        if (k < Lr) {
+          const bool live = k < limit;
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) {
+            float t = v[u][j] + bias[j];
+            if (sp) t = softplus_ref(t);
+            t = fminf(fmaxf(t, lo), hi);
+            dst[j * pitch + k] = live ? t : 0.0f;      // positions past the chunk hold zeros
+          }
+        }
+      }
+    }
+  } else {
+    // a thread always serves the same head (CS_THREADS is a multiple of CS_HT)
+    const int hh_t = tid % CS_HT;
+    const int h_t = h0 + hh_t;
+    const bool head_ok = h_t < p.nheads;
+    const float bias = (head_ok && p.dt_bias != nullptr)
+                           ? load_f(p.dt_bias, p.bias_dtype, (int64_t)h_t * p.bias_stride) : 0.0f;
+    const int64_t dt_base = (int64_t)b * p.dt_stride_b + (int64_t)c * L * p.dt_stride_l + (int64_t)h_t * p.dt_stride_h;
+    constexpr int kRowsPerPass = CS_THREADS / CS_HT;     // 16 positions per pass
+    constexpr int kUnroll = 8;                           // loads in flight per thread
+    for (int k0 = tid / CS_HT; k0 < Lr; k0 += kRowsPerPass * kUnroll) {
+      float v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int k = k0 + u * kRowsPerPass;
+        v[u] = (head_ok && k < limit) ? load_f(p.dt, p.dt_dtype, dt_base + (int64_t)k * p.dt_stride_l) : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int k = k0 + u * kRowsPerPass;
+        if (k < Lr) {
+          float t = 0.0f;
+          if (head_ok && k < limit) {
+            t = v[u] + bias;
+            if (p.dt_softplus) t = softplus_ref(t);
+            t = fminf(fmaxf(t, p.dt_min), p.dt_max);
+          }
+          tile[hh_t * pitch + k] = t;                    // positions past the chunk hold zeros
+        }
       }
     }
   }
@@ -72,38 +156,76 @@ chunk_cumsum_kernel(ssd_chunk_cumsum_params_t p, int nchunks) {
     const float a = load_f(p.A, p.A_dtype, (int64_t)h * p.A_stride);
     const int64_t obase = (((int64_t)b * p.nheads + h) * nchunks + c) * L;
     float carry = 0.0f;
-    for (int k0 = 0; k0 < L; k0 += 32) {
-      const int k = k0 + lane;
-      const float d = (k < L) ? tile[k * (CS_HT + 1) + hh] : 0.0f;
-      float s = d * a;
+    for (int k0 = 0; k0 < Lr; k0 += CS_ROUND) {
+      const int k = k0 + lane * CS_PER;
+      float d[CS_PER], s[CS_PER];
+      {
+        const float4 lo = *reinterpret_cast<const float4*>(tile + hh * pitch + k);
+        const float4 hi = *reinterpret_cast<const float4*>(tile + hh * pitch + k + 4);
+        d[0] = lo.x; d[1] = lo.y; d[2] = lo.z; d[3] = lo.w;
+        d[4] = hi.x; d[5] = hi.y; d[6] = hi.z; d[7] = hi.w;
+      }
+      float run = 0.0f;
+#pragma unroll
+      for (int i = 0; i < CS_PER; ++i) {
+        run += d[i] * a;
+        s[i] = run;
+      }
+      float incl = run;                                 // inclusive scan of the lane totals
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
-        const float t = __shfl_up_sync(0xffffffffu, s, off);
-        if (lane >= off) s += t;
+        const float t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
       }
-      s += carry;
-      if (k < L) {
-        p.dt_out[obase + k] = d;
-        p.dA_cumsum[obase + k] = s;
+      const float before = carry + (incl - run);
+#pragma unroll
+      for (int i = 0; i < CS_PER; ++i) s[i] += before;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+      if (vec && k + CS_PER <= L) {
+        float4* o1 = reinterpret_cast<float4*>(p.dt_out + obase + k);
+        float4* o2 = reinterpret_cast<float4*>(p.dA_cumsum + obase + k);
+        o1[0] = make_float4(d[0], d[1], d[2], d[3]);
+        o1[1] = make_float4(d[4], d[5], d[6], d[7]);
+        o2[0] = make_float4(s[0], s[1], s[2], s[3]);
+        o2[1] = make_float4(s[4], s[5], s[6], s[7]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < CS_PER; ++i)
+          if (k + i < L) {
+            p.dt_out[obase + k + i] = d[i];
+            p.dA_cumsum[obase + k + i] = s[i];
+          }
       }
-      carry = __shfl_sync(0xffffffffu, s, 31);
     }
   }
 }
 
 int launch_chunk_cumsum(const ssd_chunk_cumsum_params_t& p, cudaStream_t stream) {
   const int nchunks = (p.seqlen + p.chunk_size - 1) / p.chunk_size;
-  const size_t smem = (size_t)p.chunk_size * (CS_HT + 1) * sizeof(float);
+  const int pitch = (p.chunk_size + CS_ROUND - 1) / CS_ROUND * CS_ROUND + 4;
+  const size_t smem = (size_t)CS_HT * pitch * sizeof(float);
   SSD_REQUIRE(smem <= 200 * 1024, SSD_ERR_UNSUPPORTED, "chunk_size %d too large for the cumsum kernel",
               p.chunk_size);
+  // the vector path: heads contiguous, every position's head tile 16-byte aligned, whole tiles
+  const int esz = dtype_size(p.dt_dtype);
+  const bool fast = p.dt_stride_h == 1 && p.nheads % CS_HT == 0 && (reinterpret_cast<uintptr_t>(p.dt) & 15) == 0 &&
+                    (p.dt_stride_l * esz) % 16 == 0 && (p.dt_stride_b * esz) % 16 == 0;
+  void (*kern)(ssd_chunk_cumsum_params_t, int, int, int) = chunk_cumsum_kernel<float, false>;
+  if (fast) {
+    kern = p.dt_dtype == SSD_F32    ? chunk_cumsum_kernel<float, true>
+           : p.dt_dtype == SSD_BF16 ? chunk_cumsum_kernel<__nv_bfloat16, true>
+                                    : chunk_cumsum_kernel<__half, true>;
+  }
   if (smem > 48 * 1024) {
-    SSD_CUDA_OK(cudaFuncSetAttribute(chunk_cumsum_kernel,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
   SSD_REQUIRE(nchunks <= 65535 && p.batch <= 65535, SSD_ERR_UNSUPPORTED,
               "cumsum grid too large (nchunks %d, batch %d)", nchunks, p.batch);
+  // 16-byte stores need aligned output rows: aligned bases and a chunk size that keeps them so
+  const int vec = (p.chunk_size % 4 == 0) && (reinterpret_cast<uintptr_t>(p.dt_out) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(p.dA_cumsum) & 15) == 0;
   dim3 grid((p.nheads + CS_HT - 1) / CS_HT, nchunks, p.batch);
-  chunk_cumsum_kernel<<<grid, CS_THREADS, smem, stream>>>(p, nchunks);
+  kern<<<grid, CS_THREADS, smem, stream>>>(p, nchunks, pitch, vec);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }
