@@ -15,8 +15,9 @@ so the job is N x the single-GPU workload: weak scaling.
 
 Prints ONE JSON line (rank 0):
   value     tokens/s over all ranks, inputs resident in HBM, CUDA-event timed, max over ranks
-  e2e       the same calls fed from pinned HOST buffers, host->device and device->host copies
-            inside the timed region
+  e2e       the same calls fed from pinned HOST buffers, host->device and device->host copies of
+            every step inside the timed region (copies and compute of successive steps overlap
+            on three streams)
   roofline  the fused kernel alone: algorithmic bytes per launch / its mean CUDA-event time,
             against the measured HBM copy bandwidth of this pool (MEASURED_PEAKS.json)
   cpu_baseline  the same chunked math in torch on the host cores, on a bounded sample
@@ -354,31 +355,56 @@ def main():
         h_fin = torch.empty((w["batch"], w["nheads"], w["headdim"], w["dstate"]), dtype=torch.float32).pin_memory()
         h_dA = torch.empty((w["batch"], w["nheads"], nchunks, L), dtype=torch.float32).pin_memory()
         h_dt = torch.empty_like(h_dA).pin_memory()
-        dx, dB, ddt, dA_, dbias = (torch.empty_like(t) for t in (x, B, dt, A, bias))
         h2d = sum(t.numel() * t.element_size() for t in (hx, hB, hdt, hA, hbias))
         d2h = sum(t.numel() * t.element_size() for t in (h_out, h_fin, h_dA, h_dt))
+        # Three streams (copy in, compute, copy out) and two sets of device input buffers, so
+        # that step i+1's inputs cross PCIe while step i computes and step i-1's results go back.
+        # Every step still copies all of its inputs in and all of its results out.
+        dev_in = [tuple(torch.empty_like(t) for t in (x, B, dt, A, bias)) for _ in range(2)]
+        s_in, s_cmp, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        in_free = [torch.cuda.Event() for _ in range(2)]
+        done = torch.cuda.Event()
 
-        def e2e_step():
-            dx.copy_(hx, non_blocking=True)
-            dB.copy_(hB, non_blocking=True)
-            ddt.copy_(hdt, non_blocking=True)
-            dA_.copy_(hA, non_blocking=True)
-            dbias.copy_(hbias, non_blocking=True)
-            a, t_ = cumsum(ddt, dA_, L, dt_bias=dbias, dt_softplus=True)
-            o, f = fused(dB, dx, t_, a, torch.bfloat16)
-            h_out.copy_(o, non_blocking=True)
-            h_fin.copy_(f, non_blocking=True)
-            h_dA.copy_(a, non_blocking=True)
-            h_dt.copy_(t_, non_blocking=True)
+        def e2e_step(i):
+            slot = i % 2
+            dx, dB, ddt, dA_, dbias = dev_in[slot]
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(in_free[slot])          # the compute that read this slot is done
+                dx.copy_(hx, non_blocking=True)
+                dB.copy_(hB, non_blocking=True)
+                ddt.copy_(hdt, non_blocking=True)
+                dA_.copy_(hA, non_blocking=True)
+                dbias.copy_(hbias, non_blocking=True)
+                in_ready[slot].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(in_ready[slot])
+                a, t_ = cumsum(ddt, dA_, L, dt_bias=dbias, dt_softplus=True)
+                o, f = fused(dB, dx, t_, a, torch.bfloat16)
+                in_free[slot].record(s_cmp)
+                done.record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for t in (o, f, a, t_):
+                    t.record_stream(s_out)
+                h_out.copy_(o, non_blocking=True)
+                h_fin.copy_(f, non_blocking=True)
+                h_dA.copy_(a, non_blocking=True)
+                h_dt.copy_(t_, non_blocking=True)
 
         Ke = max(3, min(K, 20))
-        for _ in range(2):
-            e2e_step()
+        for i in range(2):
+            e2e_step(i)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(Ke):
-            e2e_step()
+        for st in (s_in, s_cmp, s_out):
+            st.wait_event(e0)
+        for i in range(Ke):
+            e2e_step(i + 2)
+        for st in (s_in, s_cmp, s_out):
+            torch.cuda.current_stream().wait_stream(st)
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1) / Ke
@@ -416,7 +442,8 @@ def main():
                          "frac_of_8TBs": achieved / 8000.0,
                          "cumsum_ms_per_launch": statistics.mean(cumsum_ms)},
             "e2e": {"value": world * tokens_per_rank / (e2e_ms * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": Ke},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": Ke,
+                    "overlap": "copy-in, compute and copy-out of successive steps on three streams, two input slots"},
             "gpu_launches": 2 * K,
             "clocks": clocks,
         }
