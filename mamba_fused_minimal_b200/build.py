@@ -22,7 +22,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 
-CUDA_SOURCES = ["ssd_abi.cu", "ssd_general.cu", "ssd_fused_sm100.cu", "ssd_static_scratch.cu"]
+CUDA_SOURCES = ["ssd_abi.cu", "ssd_general.cu", "ssd_fused_sm100.cu", "ssd_gemm_sm100.cu", "ssd_static_scratch.cu"]
 CUDA_HEADERS = ["ssd_common.cuh", "ssd_carry.cuh", "ssd_launch.h", "sm100_ptx.cuh", os.path.join(INCLUDE, "ssd_b200.h")]
 LIB = os.path.join(PKG, "libssd_b200.so")
 EXT = os.path.join(PKG, "_C.so")

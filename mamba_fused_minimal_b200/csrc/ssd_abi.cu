@@ -222,6 +222,7 @@ int ssd_bmm_chunk_fwd(const ssd_bmm_chunk_params_t* prm, ssd_stream_t stream) {
   SSD_REQUIRE(valid_dtype(p.in_dtype) && valid_dtype(p.out_dtype), SSD_ERR_BAD_ARGUMENT, "bad dtype");
   SSD_REQUIRE(p.batch > 0 && p.seqlen > 0 && p.ngroups > 0 && p.k > 0 && p.chunk_size > 0, SSD_ERR_BAD_ARGUMENT,
               "sizes must be positive");
+  if (bmm_fast_ok(p)) return launch_bmm_chunk_fast(p, reinterpret_cast<cudaStream_t>(stream));
   return launch_bmm_chunk_general(p, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -779,22 +779,9 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 4-D map over a (b, l, heads, inner) tensor whose innermost dimension is contiguous;
-// box = 64 inner elements x 1 head x kKT positions x 1 batch, 128-byte swizzle.
 int make_map(CUtensorMap* map, const void* base, int dtype, int inner, int heads, int seqlen, int batch,
              const int64_t* stride /* b, l, h, inner */) {
-  EncodeTiledFn enc = get_encode_fn();
-  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  const cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)heads, (cuuint64_t)seqlen, (cuuint64_t)batch};
-  const cuuint64_t strides[3] = {(cuuint64_t)stride[2] * 2, (cuuint64_t)stride[1] * 2, (cuuint64_t)stride[0] * 2};
-  const cuuint32_t box[4] = {64, 1, (cuuint32_t)kKT, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUtensorMapDataType dt = dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return SSD_OK;
+  return make_rows_map(map, base, dtype, inner, heads, seqlen, batch, stride, kKT);
 }
 
 // 5-D map over the 16-bit passed states (b, c, h, p, n) with (p, n) dense; box = 32 columns (one
@@ -925,6 +912,21 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
 
 }  // namespace
 
+int make_rows_map(CUtensorMap* map, const void* base, int dtype, int inner, int heads, int seqlen, int batch,
+                  const int64_t* stride /* b, l, h, inner */, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)heads, (cuuint64_t)seqlen, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)stride[2] * 2, (cuuint64_t)stride[1] * 2, (cuuint64_t)stride[0] * 2};
+  const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
 
 int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why) {
   const ssd_state_inputs_t& in = p.in;

@@ -1,6 +1,7 @@
 // Internal launch interface between the C ABI (ssd_abi.cu) and the kernel files.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "ssd_b200.h"
@@ -29,5 +30,15 @@ int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why);
 size_t fused_fast_workspace_bytes(const ssd_fused_state_params_t& p);
 // mode 0: chunk state + state passing; mode 1: per-chunk states only (p.states required).
 int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream);
+
+// 4-D tensor map over a 16-bit (b, l, heads, inner) tensor whose innermost dimension is
+// contiguous (strides in elements: b, l, heads, inner); box = 64 inner elements x 1 head x
+// box_rows positions x 1 batch element, 128-byte swizzle.
+int make_rows_map(CUtensorMap* map, const void* base, int dtype, int inner, int heads, int seqlen, int batch,
+                  const int64_t* stride, int box_rows);
+
+// ---- tcgen05 chunk bmm (ssd_gemm_sm100.cu) --------------------------------------------
+int bmm_fast_ok(const ssd_bmm_chunk_params_t& p);
+int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream);
 
 }  // namespace ssd
