@@ -238,6 +238,7 @@ int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t stream) 
   SSD_REQUIRE(p.batch > 0 && p.seqlen > 0 && p.nheads > 0 && p.headdim > 0 && p.ngroups > 0 && p.dstate > 0 &&
                   p.chunk_size > 0 && p.nheads % p.ngroups == 0,
               SSD_ERR_BAD_ARGUMENT, "bad sizes");
+  if (scan_fast_ok(p)) return launch_chunk_scan_fast(p, reinterpret_cast<cudaStream_t>(stream));
   return launch_chunk_scan_general(p, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -928,6 +928,23 @@ int make_rows_map(CUtensorMap* map, const void* base, int dtype, int inner, int 
   return SSD_OK;
 }
 
+int make_states_map(CUtensorMap* map, const void* base, int dtype, int nheads, int nchunks, int batch,
+                    const int64_t* stride /* b, c, h */) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[5] = {(cuuint64_t)kN, (cuuint64_t)kP, (cuuint64_t)nheads, (cuuint64_t)nchunks, (cuuint64_t)batch};
+  const cuuint64_t strides[4] = {(cuuint64_t)kN * 2, (cuuint64_t)stride[2] * 2, (cuuint64_t)stride[1] * 2,
+                                 (cuuint64_t)stride[0] * 2};
+  const cuuint32_t box[5] = {64, (cuuint32_t)kP, 1, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 5, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled (states) failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
+
 int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why) {
   const ssd_state_inputs_t& in = p.in;
   auto no = [&](const char* m) { if (why) *why = m; return 0; };

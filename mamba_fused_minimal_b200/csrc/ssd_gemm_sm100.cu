@@ -25,6 +25,30 @@ template <typename T> struct Pack16;
 template <> struct Pack16<__nv_bfloat16> { static constexpr uint32_t kFmt = 1; };
 template <> struct Pack16<__half> { static constexpr uint32_t kFmt = 0; };
 
+// Two 16-bit values in one 32-bit word, low half first.
+template <typename T> struct PackPair;
+template <> struct PackPair<__nv_bfloat16> {
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __device__ static __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  }
+};
+template <> struct PackPair<__half> {
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __device__ static __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+};
+
 constexpr int kBmmRows = 128;        // rows i per CTA (the MMA's M)
 constexpr int kBmmThreads = 160;     // 4 epilogue warps + 1 service warp
 
@@ -139,6 +163,246 @@ bmm_chunk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
+
+// =====================================================================================
+// chunk scan (the reference's _chunk_scan_fwd, kernels/ssd_chunk_scan.py:38-169)
+// =====================================================================================
+// CTA = 128 positions m of one (batch, chunk, head) x the 64 headdim columns.
+//   acc1[m, p] = sum_n C[m, n] * state[p, n]            SS MMA, both operands K-major from TMA
+//   acc2[m, p] = sum_{k <= m} A2[m, k] * x[k, p]        A2 from tensor memory, x as TMA delivers it
+//   A2[m, k]   = cast_x(cb[m, k] * exp(min(a_m - a_k, 0)) * dt_k)   (the reference's rounding point)
+//   out[m, p]  = exp(a_m) * acc1 + acc2 + D * x[m, p]
+// Warps 0-3 own one row m per thread (= one TMEM lane): they build A2 in 64-position blocks
+// straight from their cb row (two slots in tensor memory, tcgen05.st), then run the epilogue.
+// Warp 4: one thread issues every TMA load and MMA.  Blocks of positions above the diagonal
+// are never touched.
+constexpr int kScanRows = 128;
+constexpr int kScanThreads = 160;
+constexpr int kScanKB = 64;            // positions per A2 block
+constexpr int kScanP = 64;             // headdim
+constexpr int kScanN = 128;            // dstate
+
+enum ScanWait { kScanWaitCS = 301, kScanWaitX, kScanWaitAReady, kScanWaitAFree, kScanWaitAcc };
+
+struct ScanArgs {
+  const float* cb;
+  const float* dt;
+  const float* dA;
+  const void* D;
+  void* out;
+  int* status;
+  int64_t cb_s[4];                     // b, c, g, m (k stride is 1)
+  int64_t dt_s[3], dA_s[3];            // b, h, c (L stride is 1)
+  int64_t out_s[3];                    // b, l, h (p stride is 1)
+  int64_t D_stride;
+  int D_dtype, D_has_hdim, out_dtype;
+  int L, seqlen, nheads, ngroups, nchunks;
+};
+
+__device__ int g_scan_status[4];
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_constant__ CUtensorMap tmap_S,
+                  const __grid_constant__ CUtensorMap tmap_x, const ScanArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int L = a.L;
+  // shared-memory map
+  constexpr uint32_t kCBox = kScanRows * 128, kSBox = kScanP * 128, kXBox = kScanKB * 128;
+  constexpr uint32_t kOffS = 2 * kCBox, kOffX = kOffS + 2 * kSBox, kOffVec = kOffX + 4 * kXBox;
+  constexpr uint32_t kOffCtl = kOffVec + 2 * 256 * 4;
+  float* dA_s = reinterpret_cast<float*>(smem + kOffVec);
+  float* dt_s = dA_s + 256;
+  const uint32_t bars = sbase + kOffCtl;
+  const uint32_t bar_cs = bars, bar_acc = bars + 8;
+  auto bar_x = [&](int i) { return bars + 16 + 8u * i; };
+  auto bar_a_ready = [&](int i) { return bars + 48 + 8u * i; };
+  auto bar_a_free = [&](int i) { return bars + 64 + 8u * i; };
+  volatile int* ctl = reinterpret_cast<volatile int*>(smem + kOffCtl + 80);     // [0] abort, [1] tmem
+  WaitCtx wc{ctl, a.status};
+
+  const int mt = blockIdx.x;                       // 128-row tile inside the chunk
+  const int h = blockIdx.y;
+  const int b = blockIdx.z / a.nchunks, c = blockIdx.z % a.nchunks;
+  const int g = h / (a.nheads / a.ngroups);
+  const int limit = min(L, a.seqlen - c * L);      // valid positions of this chunk
+  // 64-position blocks this tile needs: up to its own diagonal, and only those that hold data
+  const int nkb = min(2 * (mt + 1), (limit + kScanKB - 1) / kScanKB);
+
+  if (tid == 0) {
+    mbar_init(bar_cs, 1);
+    mbar_init(bar_acc, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(bar_x(i), 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_a_ready(i), 4); mbar_init(bar_a_free(i), 1); }
+    ctl[0] = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 4) {
+    tmem_alloc(sbase + kOffCtl + 84, 256);
+    tmem_relinquish();
+  } else {
+    // this chunk's cumulative log-decay and dt rows
+    const float* dAr = a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2];
+    const float* dtr = a.dt + (int64_t)b * a.dt_s[0] + (int64_t)h * a.dt_s[1] + (int64_t)c * a.dt_s[2];
+    for (int k = tid; k < L; k += 128) {
+      dA_s[k] = dAr[k];
+      dt_s[k] = dtr[k];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = static_cast<uint32_t>(ctl[1]);
+  constexpr uint32_t kAcc1 = 0, kAcc2 = 64, kA2 = 128;       // TMEM columns
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(bar_cs, 2 * kCBox + 2 * kSBox);
+      for (int kb = 0; kb < 2; ++kb) {
+        tma_load_4d(sbase + kb * kCBox, &tmap_C, bar_cs, kb * 64, g, c * L + mt * kScanRows, b);
+        tma_load_5d(sbase + kOffS + kb * kSBox, &tmap_S, bar_cs, kb * 64, 0, h, c, b);
+      }
+      for (int kb = 0; kb < nkb; ++kb) {
+        mbar_expect_tx(bar_x(kb), kXBox);
+        tma_load_4d(sbase + kOffX + kb * kXBox, &tmap_x, bar_x(kb), 0, h, c * L + kb * kScanKB, b);
+      }
+      bool ok = mbar_wait(bar_cs, 0, wc, kScanWaitCS);
+      if (ok) {
+        tc_fence_after();
+        // acc1 = C . state^T: both K-major (dstate contiguous), 128-byte swizzle
+        const uint32_t idesc1 = mma_idesc(Pack16<T>::kFmt, false, false, kScanRows, kScanP);
+        for (int k16 = 0; k16 < kScanN / 16; ++k16) {
+          const uint32_t koff = (k16 & 3) * 32;
+          const uint64_t ad = smem_desc_sw128(sbase + (k16 >> 2) * kCBox + koff, 16, 1024);
+          const uint64_t bd = smem_desc_sw128(sbase + kOffS + (k16 >> 2) * kSBox + koff, 16, 1024);
+          mma_f16_ss(tmem_base + kAcc1, ad, bd, idesc1, k16 != 0 ? 1u : 0u);
+        }
+        // acc2 += A2 . x: A2 from tensor memory (K-major by construction), x MN-major as loaded
+        const uint32_t idesc2 = mma_idesc(Pack16<T>::kFmt, false, true, kScanRows, kScanP);
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          ok = mbar_wait(bar_x(kb), 0, wc, kScanWaitX);
+          if (!ok) break;
+          ok = mbar_wait(bar_a_ready(kb & 1), (kb >> 1) & 1, wc, kScanWaitAReady);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t bd0 = smem_desc_sw128(sbase + kOffX + kb * kXBox, kXBox, 1024);
+          for (int k16 = 0; k16 < kScanKB / 16; ++k16)
+            mma_f16_ts(tmem_base + kAcc2, tmem_base + kA2 + (kb & 1) * 32 + k16 * 8, bd0 + (uint64_t)((k16 * 2048) >> 4),
+                       idesc2, (kb | k16) != 0 ? 1u : 0u);
+          mma_commit(bar_a_free(kb & 1));
+        }
+        if (ok) mma_commit(bar_acc);
+      }
+    }
+  } else {
+    const int r = tid;                               // row of the tile = TMEM lane
+    const int m = mt * kScanRows + r;                // position inside the chunk
+    const float am = dA_s[min(m, L - 1)];
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const float* cbrow = a.cb + (int64_t)b * a.cb_s[0] + (int64_t)c * a.cb_s[1] + (int64_t)g * a.cb_s[2] + (int64_t)m * a.cb_s[3];
+    bool ok = true;
+    for (int kb = 0; kb < nkb && ok; ++kb) {
+      ok = mbar_wait(bar_a_free(kb & 1), ((kb >> 1) & 1) ^ 1, wc, kScanWaitAFree);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int k0 = kb * kScanKB + half * 32;
+        uint32_t o[16];
+        if (k0 > m || m >= L) {                      // wholly above the diagonal (or a row past the chunk)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = 0u;
+        } else {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(cbrow + k0) + i);
+            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int k = k0 + i;
+            float w = v[i] * fast_exp(fminf(am - dA_s[k], 0.0f));
+            w *= dt_s[k];
+            v[i] = (k <= m) ? w : 0.0f;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = PackPair<T>::pack(v[2 * i], v[2 * i + 1]);
+        }
+        tmem_st_32x32b_x16(tmem_base + lane_sel + kA2 + (kb & 1) * 32 + half * 16, o);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_a_ready(kb & 1));
+    }
+    // ---- epilogue: out = exp(a_m) * acc1 + acc2 + D * x[m]
+    if (ok) ok = mbar_wait(bar_acc, 0, wc, kScanWaitAcc, 64);
+    const bool live = m < limit;
+    // the x block that holds position m is read below with ordinary loads: observe its barrier
+    if (ok && live && a.D != nullptr) ok = mbar_wait(bar_x(m / kScanKB), 0, wc, kScanWaitX);
+    if (ok) {
+      tc_fence_after();
+      const float sm = fast_exp(am);
+      const float dh = (a.D != nullptr && !a.D_has_hdim) ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride) : 0.0f;
+      // x[m, :] sits in the x block that holds position m: row m % 64, 16-byte pieces swizzled by row % 8
+      const uint8_t* xrow = smem + kOffX + (m / kScanKB) * kXBox + (m % kScanKB) * 128;
+      const int xs = m & 7;
+      uint8_t* orow = static_cast<uint8_t*>(a.out) +
+                      2 * ((int64_t)b * a.out_s[0] + (int64_t)(c * L + m) * a.out_s[1] + (int64_t)h * a.out_s[2]);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint32_t r1[32], r2[32];
+        tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
+        tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
+        tmem_ld_wait();
+        float res[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) res[i] = fmaf(__uint_as_float(r1[i]), sm, 0.0f) + __uint_as_float(r2[i]);
+        if (a.D != nullptr && live) {
+#pragma unroll
+          for (int pc = 0; pc < 4; ++pc) {           // 16-byte pieces = 8 headdim columns
+            const int piece = q * 4 + pc;
+            const uint4 t = *reinterpret_cast<const uint4*>(xrow + ((piece ^ xs) << 4));
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float x0, x1;
+              PackPair<T>::unpack(w[i], x0, x1);
+              const int pcol = piece * 8 + 2 * i;
+              const float d0 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol) : dh;
+              const float d1 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol + 1) : dh;
+              res[pc * 8 + 2 * i] += x0 * d0;
+              res[pc * 8 + 2 * i + 1] += x1 * d1;
+            }
+          }
+        }
+        if (live) {
+#pragma unroll
+          for (int pc = 0; pc < 4; ++pc) {
+            uint4 t;
+            t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
+            t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
+            t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
+            t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
+            *reinterpret_cast<uint4*>(orow + (q * 4 + pc) * 16) = t;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
 }  // namespace
 
 // 1 if the tcgen05 kernel takes this problem (otherwise the plain kernel does).
@@ -181,6 +445,68 @@ int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream) 
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kBmmRows, nchunks * p.ngroups, p.batch);
   kern<<<grid, kBmmThreads, smem, stream>>>(ma, mb, a);
+  SSD_CUDA_OK(cudaGetLastError());
+  return SSD_OK;
+}
+
+
+// 1 if the tcgen05 chunk-scan kernel takes this problem (otherwise the plain kernel does).
+int scan_fast_ok(const ssd_chunk_scan_params_t& p) {
+  if (p.in_dtype != SSD_BF16 && p.in_dtype != SSD_F16) return 0;
+  if (p.states_dtype != p.in_dtype || p.cb_dtype != SSD_F32) return 0;
+  if (p.z != nullptr || p.seq_idx != nullptr) return 0;
+  if (p.headdim != kScanP || p.dstate != kScanN) return 0;
+  if (p.chunk_size != 128 && p.chunk_size != 256) return 0;
+  if (p.x_stride[3] != 1 || p.C_stride[3] != 1 || p.states_stride[4] != 1 || p.out_stride[3] != 1 || p.cb_stride[4] != 1 ||
+      p.dt_stride[3] != 1 || p.dA_stride[3] != 1)
+    return 0;
+  if (p.states_stride[3] != kScanN) return 0;                            // (p, n) dense
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!al16(p.x) || !al16(p.C) || !al16(p.states) || !al16(p.out) || !al16(p.cb)) return 0;
+  for (int i = 0; i < 3; ++i)
+    if (p.x_stride[i] % 8 != 0 || p.C_stride[i] % 8 != 0 || p.out_stride[i] % 8 != 0) return 0;
+  for (int i = 0; i < 3; ++i)
+    if (p.states_stride[i] % 8 != 0) return 0;
+  for (int i = 0; i < 4; ++i)
+    if (p.cb_stride[i] % 4 != 0) return 0;
+  if (p.nheads > 65535) return 0;
+  return 1;
+}
+
+int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream) {
+  const int L = p.chunk_size;
+  const int nchunks = (p.seqlen + L - 1) / L;
+  SSD_REQUIRE((long long)p.batch * nchunks <= 65535, SSD_ERR_UNSUPPORTED, "chunk scan grid too large");
+  CUtensorMap mC, mS, mx;
+  int rc = make_rows_map(&mC, p.C, p.in_dtype, p.dstate, p.ngroups, p.seqlen, p.batch, p.C_stride, kScanRows);
+  if (rc != SSD_OK) return rc;
+  rc = make_rows_map(&mx, p.x, p.in_dtype, p.headdim, p.nheads, p.seqlen, p.batch, p.x_stride, kScanKB);
+  if (rc != SSD_OK) return rc;
+  rc = make_states_map(&mS, p.states, p.in_dtype, p.nheads, nchunks, p.batch, p.states_stride);
+  if (rc != SSD_OK) return rc;
+  ScanArgs a{};
+  a.cb = static_cast<const float*>(p.cb);
+  a.dt = p.dt;
+  a.dA = p.dA_cumsum;
+  a.D = p.D;
+  a.out = p.out;
+  SSD_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&a.status), g_scan_status));
+  for (int i = 0; i < 4; ++i) a.cb_s[i] = p.cb_stride[i];
+  for (int i = 0; i < 3; ++i) { a.dt_s[i] = p.dt_stride[i]; a.dA_s[i] = p.dA_stride[i]; a.out_s[i] = p.out_stride[i]; }
+  a.D_stride = p.D_stride;
+  a.D_dtype = p.D_dtype;
+  a.D_has_hdim = p.D_has_hdim;
+  a.out_dtype = p.in_dtype;
+  a.L = L;
+  a.seqlen = p.seqlen;
+  a.nheads = p.nheads;
+  a.ngroups = p.ngroups;
+  a.nchunks = nchunks;
+  const int smem = 2 * kScanRows * 128 + 2 * kScanP * 128 + 4 * kScanKB * 128 + 2 * 256 * 4 + 128 + 1024;
+  auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_kernel<__nv_bfloat16> : chunk_scan_kernel<__half>;
+  SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
+  kern<<<grid, kScanThreads, smem, stream>>>(mC, mS, mx, a);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }

@@ -37,8 +37,15 @@ int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t 
 int make_rows_map(CUtensorMap* map, const void* base, int dtype, int inner, int heads, int seqlen, int batch,
                   const int64_t* stride, int box_rows);
 
-// ---- tcgen05 chunk bmm (ssd_gemm_sm100.cu) --------------------------------------------
+// 5-D tensor map over 16-bit passed states (b, c, h, p, n) with (p, n) dense (strides in
+// elements: b, c, h); box = 64 n x 64 p, 128-byte swizzle.
+int make_states_map(CUtensorMap* map, const void* base, int dtype, int nheads, int nchunks, int batch,
+                    const int64_t* stride);
+
+// ---- tcgen05 chunk bmm and chunk scan (ssd_gemm_sm100.cu) -----------------------------
 int bmm_fast_ok(const ssd_bmm_chunk_params_t& p);
 int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream);
+int scan_fast_ok(const ssd_chunk_scan_params_t& p);
+int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream);
 
 }  // namespace ssd

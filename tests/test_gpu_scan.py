@@ -1,0 +1,52 @@
+"""_chunk_scan_fwd on the GPU against the oracle: the shapes the tcgen05 kernel takes (16-bit
+inputs and passed states, fp32 cb, headdim 64, dstate 128, chunk 128 / 256, no z / seq_idx)
+and the same data through the plain kernel."""
+import pytest
+import torch
+
+from oracle import ssd_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(device, dtype, b, l, h, g, L, seed, d_hdim=False, with_d=True):
+    from mamba_fused_minimal_b200.kernels.fused_concurrent import _fused_chunk_state_state_passing_fwd_concurrent as fused
+    from mamba_fused_minimal_b200.kernels.ssd_bmm import _bmm_chunk_fwd
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_state import _chunk_cumsum_fwd
+    inp = O.make_inputs(b, l, h, 64, g, 128, dtype=dtype, seed=seed)
+    d = {k: v.to(device) for k, v in inp.items()}
+    dA, dt = _chunk_cumsum_fwd(d["dt"], d["A"], L, dt_bias=d["dt_bias"], dt_softplus=True)
+    passed, _ = fused(d["B"], d["x"], dt, dA, dtype)
+    cb = _bmm_chunk_fwd(d["C"], d["B"], L, output_dtype=torch.float32)
+    D = None
+    if with_d:
+        D = torch.randn(h, 64) if d_hdim else inp["D"]
+    return inp, d, dA, dt, passed, cb, D
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,l,h,g,L,d_hdim,with_d", [(2, 1024, 4, 1, 256, False, True), (1, 700, 6, 2, 256, True, True),
+                                                      (2, 384, 2, 2, 128, False, False), (1, 130, 2, 1, 128, False, True)])
+def test_chunk_scan_against_oracle(cuda_device, dtype, b, l, h, g, L, d_hdim, with_d):
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _chunk_scan_fwd
+    inp, d, dA, dt, passed, cb, D = _case(cuda_device, dtype, b, l, h, g, L, seed=l + h, d_hdim=d_hdim, with_d=with_d)
+    out, _ = _chunk_scan_fwd(cb, d["x"], dt, dA, d["C"], passed, D=None if D is None else D.to(cuda_device))
+    ref, _ = O.chunk_scan_fwd(cb.cpu(), inp["x"], dt.cpu(), dA.cpu(), inp["C"], passed.cpu(), D=D, exp_impl="ex2")
+    scale = ref.float().abs().max()
+    torch.testing.assert_close(out.float().cpu() / scale, ref.float() / scale, atol=1e-2, rtol=1e-2)
+    assert torch.isfinite(out).all()
+
+
+def test_chunk_scan_fast_and_plain_kernels_agree(cuda_device):
+    """The same data through the tcgen05 kernel and, forced by an all-zero seq_idx (one
+    sequence, no boundary), through the plain kernel."""
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _chunk_scan_fwd
+    inp, d, dA, dt, passed, cb, D = _case(cuda_device, torch.bfloat16, 2, 1024, 8, 1, 256, seed=3)
+    D = D.to(cuda_device)
+    out_f, _ = _chunk_scan_fwd(cb, d["x"], dt, dA, d["C"], passed, D=D)
+    si = torch.zeros(2, 1024, dtype=torch.int32, device=cuda_device)
+    out_p, _ = _chunk_scan_fwd(cb, d["x"], dt, dA, d["C"], passed, D=D, seq_idx=si)
+    scale = out_p.float().abs().max()
+    # identical rounding points; only the order of the fp32 additions differs
+    assert ((out_f.float() - out_p.float()).abs().max() / scale).item() <= 1e-2
+    assert (out_f == out_p).float().mean().item() > 0.99
