@@ -172,12 +172,14 @@ bmm_chunk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 //   acc2[m, p] = sum_{k <= m} A2[m, k] * x[k, p]        A2 from tensor memory, x as TMA delivers it
 //   A2[m, k]   = cast_x(cb[m, k] * exp(min(a_m - a_k, 0)) * dt_k)   (the reference's rounding point)
 //   out[m, p]  = exp(a_m) * acc1 + acc2 + D * x[m, p]
-// Warps 0-3 own one row m per thread (= one TMEM lane): they build A2 in 64-position blocks
-// straight from their cb row (two slots in tensor memory, tcgen05.st), then run the epilogue.
-// Warp 4: one thread issues every TMA load and MMA.  Blocks of positions above the diagonal
-// are never touched.
+// Warps 0-7: a thread owns one row m (= one TMEM lane; warp w covers lanes 32 (w % 4) ..) and
+// one half (w / 4) of every 64-position block: it builds that half of A2 straight from its cb
+// row (two slots in tensor memory, tcgen05.st) and later runs the epilogue for the same half of
+// the headdim columns.  Warp 8: one thread issues every TMA load and MMA.  Blocks of positions
+// above the diagonal are never touched.
 constexpr int kScanRows = 128;
-constexpr int kScanThreads = 160;
+constexpr int kScanRowWarps = 8;
+constexpr int kScanThreads = (kScanRowWarps + 1) * 32;
 constexpr int kScanKB = 64;            // positions per A2 block
 constexpr int kScanP = 64;             // headdim
 constexpr int kScanN = 128;            // dstate
@@ -236,19 +238,19 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
     mbar_init(bar_cs, 1);
     mbar_init(bar_acc, 1);
     for (int i = 0; i < 4; ++i) mbar_init(bar_x(i), 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_a_ready(i), 4); mbar_init(bar_a_free(i), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_a_ready(i), kScanRowWarps); mbar_init(bar_a_free(i), 1); }
     ctl[0] = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
   }
-  if (warp == 4) {
+  if (warp == kScanRowWarps) {
     tmem_alloc(sbase + kOffCtl + 84, 256);
     tmem_relinquish();
   } else {
     // this chunk's cumulative log-decay and dt rows
     const float* dAr = a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2];
     const float* dtr = a.dt + (int64_t)b * a.dt_s[0] + (int64_t)h * a.dt_s[1] + (int64_t)c * a.dt_s[2];
-    for (int k = tid; k < L; k += 128) {
+    for (int k = tid; k < L; k += kScanRowWarps * 32) {
       dA_s[k] = dAr[k];
       dt_s[k] = dtr[k];
     }
@@ -259,7 +261,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
   const uint32_t tmem_base = static_cast<uint32_t>(ctl[1]);
   constexpr uint32_t kAcc1 = 0, kAcc2 = 64, kA2 = 128;       // TMEM columns
 
-  if (warp == 4) {
+  if (warp == kScanRowWarps) {
     if (lane == 0) {
       mbar_expect_tx(bar_cs, 2 * kCBox + 2 * kSBox);
       for (int kb = 0; kb < 2; ++kb) {
@@ -299,21 +301,21 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
       }
     }
   } else {
-    const int r = tid;                               // row of the tile = TMEM lane
+    const int r = (warp & 3) * 32 + lane;            // row of the tile = TMEM lane
+    const int half = warp >> 2;                      // which 32 positions of a block / which 32 headdim columns
     const int m = mt * kScanRows + r;                // position inside the chunk
     const float am = dA_s[min(m, L - 1)];
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float* cbrow = a.cb + (int64_t)b * a.cb_s[0] + (int64_t)c * a.cb_s[1] + (int64_t)g * a.cb_s[2] + (int64_t)m * a.cb_s[3];
     bool ok = true;
     for (int kb = 0; kb < nkb && ok; ++kb) {
       ok = mbar_wait(bar_a_free(kb & 1), ((kb >> 1) & 1) ^ 1, wc, kScanWaitAFree);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         const int k0 = kb * kScanKB + half * 32;
         uint32_t o[16];
-        if (k0 > m || m >= L) {                      // wholly above the diagonal (or a row past the chunk)
+        if (k0 > m) {                                // wholly above the diagonal
 #pragma unroll
           for (int i = 0; i < 16; ++i) o[i] = 0u;
         } else {
@@ -354,8 +356,8 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
       const int xs = m & 7;
       uint8_t* orow = static_cast<uint8_t*>(a.out) +
                       2 * ((int64_t)b * a.out_s[0] + (int64_t)(c * L + m) * a.out_s[1] + (int64_t)h * a.out_s[2]);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
+      {
+        const int q = half;
         uint32_t r1[32], r2[32];
         tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
         tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
@@ -397,7 +399,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kScanRowWarps) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }
