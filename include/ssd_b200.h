@@ -188,9 +188,10 @@ SSD_API size_t ssd_fused_state_workspace_bytes(const ssd_fused_state_params_t* p
 SSD_API int ssd_fused_state_fwd(const ssd_fused_state_params_t* prm, ssd_stream_t stream);
 
 /* Reads back (synchronously, after synchronising `stream`) the status word that the last
- * ssd_fused_state_fwd on this workspace left: SSD_OK, or SSD_ERR_TIMEOUT if a bounded
- * device wait gave up (outputs are then incomplete).  Optional: a healthy run never sets
- * it.  Has no counterpart in the reference, whose waits are unbounded
+ * ssd_fused_state_fwd on this workspace left, and the library-held status of the tcgen05
+ * chunk bmm / chunk scan kernels on the current device: SSD_OK, or SSD_ERR_TIMEOUT if a
+ * bounded device wait gave up (outputs are then incomplete).  Optional: a healthy run never
+ * sets it.  Has no counterpart in the reference, whose waits are unbounded
  * (kernels/fused_concurrent.py:82-84,205-208). */
 SSD_API int ssd_check_status(void* workspace, ssd_stream_t stream);
 

@@ -197,10 +197,21 @@ int ssd_check_status(void* workspace, ssd_stream_t stream) {
   SSD_CUDA_OK(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
   int status = 0;
   SSD_CUDA_OK(cudaMemcpy(&status, workspace, sizeof(int), cudaMemcpyDeviceToHost));
-  if (status == 0) return SSD_OK;
-  set_error("a bounded device-side wait gave up (wait code %d); outputs are incomplete and the "
-            "workspace header must be cleared before reuse", status);
-  return SSD_ERR_TIMEOUT;
+  if (status != 0) {
+    set_error("a bounded device-side wait gave up (wait code %d); outputs are incomplete and the "
+              "workspace header must be cleared before reuse", status);
+    return SSD_ERR_TIMEOUT;
+  }
+  // the chunk bmm / chunk scan kernels keep their wait status in the library (they use no workspace)
+  int gemm_code = 0;
+  const int rc = gemm_wait_status(&gemm_code);
+  if (rc != SSD_OK) return rc;
+  if (gemm_code != 0) {
+    set_error("a bounded device-side wait of the chunk bmm / chunk scan kernels gave up (wait code %d); "
+              "their outputs are incomplete", gemm_code);
+    return SSD_ERR_TIMEOUT;
+  }
+  return SSD_OK;
 }
 
 int ssd_seqpar_fixup(const ssd_seqpar_fixup_params_t* prm, ssd_stream_t stream) {

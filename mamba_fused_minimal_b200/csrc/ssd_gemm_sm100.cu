@@ -407,6 +407,19 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
 
 }  // namespace
 
+int gemm_wait_status(int* code) {
+  int bs[4] = {0, 0, 0, 0}, ss[4] = {0, 0, 0, 0};
+  SSD_CUDA_OK(cudaMemcpyFromSymbol(bs, g_bmm_status, sizeof(bs)));
+  SSD_CUDA_OK(cudaMemcpyFromSymbol(ss, g_scan_status, sizeof(ss)));
+  *code = bs[0] != 0 ? bs[0] : ss[0];
+  if (*code != 0) {
+    const int zero[4] = {0, 0, 0, 0};
+    SSD_CUDA_OK(cudaMemcpyToSymbol(g_bmm_status, zero, sizeof(zero)));
+    SSD_CUDA_OK(cudaMemcpyToSymbol(g_scan_status, zero, sizeof(zero)));
+  }
+  return SSD_OK;
+}
+
 // 1 if the tcgen05 kernel takes this problem (otherwise the plain kernel does).
 int bmm_fast_ok(const ssd_bmm_chunk_params_t& p) {
   if (p.in_dtype != SSD_BF16 && p.in_dtype != SSD_F16) return 0;

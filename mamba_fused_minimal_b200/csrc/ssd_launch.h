@@ -45,6 +45,9 @@ int make_states_map(CUtensorMap* map, const void* base, int dtype, int nheads, i
 // ---- tcgen05 chunk bmm and chunk scan (ssd_gemm_sm100.cu) -----------------------------
 int bmm_fast_ok(const ssd_bmm_chunk_params_t& p);
 int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream);
+// Reads (and clears) the wait status words of the two kernels on the current device; *code = 0
+// when no wait gave up.  The caller has synchronised the stream.
+int gemm_wait_status(int* code);
 int scan_fast_ok(const ssd_chunk_scan_params_t& p);
 int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream);
 
