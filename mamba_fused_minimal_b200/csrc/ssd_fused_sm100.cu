@@ -945,6 +945,22 @@ int make_states_map(CUtensorMap* map, const void* base, int dtype, int nheads, i
   return SSD_OK;
 }
 
+int make_cb_map(CUtensorMap* map, const void* base, int L, int ngroups, int nchunks, int batch, const int64_t* stride,
+                int box_k, int box_m) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[5] = {(cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)ngroups, (cuuint64_t)nchunks, (cuuint64_t)batch};
+  const cuuint64_t strides[4] = {(cuuint64_t)stride[3] * 4, (cuuint64_t)stride[2] * 4, (cuuint64_t)stride[1] * 4,
+                                 (cuuint64_t)stride[0] * 4};
+  const cuuint32_t box[5] = {(cuuint32_t)box_k, (cuuint32_t)box_m, 1, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled (cb) failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
+
 int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why) {
   const ssd_state_inputs_t& in = p.in;
   auto no = [&](const char* m) { if (why) *why = m; return 0; };

@@ -172,57 +172,64 @@ bmm_chunk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 //   acc2[m, p] = sum_{k <= m} A2[m, k] * x[k, p]        A2 from tensor memory, x as TMA delivers it
 //   A2[m, k]   = cast_x(cb[m, k] * exp(min(a_m - a_k, 0)) * dt_k)   (the reference's rounding point)
 //   out[m, p]  = exp(a_m) * acc1 + acc2 + D * x[m, p]
+// The positions k are walked in units of 32.  A ring of three shared-memory slots takes, per
+// unit, the 128 x 32 fp32 tile of cb and the 32 x 64 tile of x (TMA, 128-byte swizzle).
 // Warps 0-7: a thread owns one row m (= one TMEM lane; warp w covers lanes 32 (w % 4) ..) and
-// one half (w / 4) of every 64-position block: it builds that half of A2 straight from its cb
-// row (two slots in tensor memory, tcgen05.st) and later runs the epilogue for the same half of
-// the headdim columns.  Warp 8: one thread issues every TMA load and MMA.  Blocks of positions
-// above the diagonal are never touched.
+// 16 of a unit's 32 positions (w / 4): it reads them from the staged cb tile, applies decay, dt
+// and the k <= m mask in fp32, rounds to the input type and writes them to one of two A2 slots
+// in tensor memory (tcgen05.st); afterwards it runs the epilogue for 32 of the 64 headdim
+// columns.  Warp 8: one thread issues every TMA load and MMA.  Units wholly above the
+// diagonal are never touched.
 constexpr int kScanRows = 128;
 constexpr int kScanRowWarps = 8;
 constexpr int kScanThreads = (kScanRowWarps + 1) * 32;
-constexpr int kScanKB = 64;            // positions per A2 block
+constexpr int kScanU = 32;             // positions per unit
+constexpr int kScanSlots = 3;          // ring depth
 constexpr int kScanP = 64;             // headdim
 constexpr int kScanN = 128;            // dstate
 
-enum ScanWait { kScanWaitCS = 301, kScanWaitX, kScanWaitAReady, kScanWaitAFree, kScanWaitAcc };
+enum ScanWait { kScanWaitCS = 301, kScanWaitFull, kScanWaitAReady, kScanWaitFree, kScanWaitAcc };
 
 struct ScanArgs {
-  const float* cb;
+  const void* x;
   const float* dt;
   const float* dA;
   const void* D;
   void* out;
   int* status;
-  int64_t cb_s[4];                     // b, c, g, m (k stride is 1)
+  int64_t x_s[3];                      // b, l, h (p stride is 1)
   int64_t dt_s[3], dA_s[3];            // b, h, c (L stride is 1)
   int64_t out_s[3];                    // b, l, h (p stride is 1)
   int64_t D_stride;
-  int D_dtype, D_has_hdim, out_dtype;
+  int D_dtype, D_has_hdim;
   int L, seqlen, nheads, ngroups, nchunks;
 };
 
 __device__ int g_scan_status[4];
 
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kScanThreads, 2)
 chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_constant__ CUtensorMap tmap_S,
-                  const __grid_constant__ CUtensorMap tmap_x, const ScanArgs a) {
+                  const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_cb,
+                  const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int L = a.L;
   // shared-memory map
-  constexpr uint32_t kCBox = kScanRows * 128, kSBox = kScanP * 128, kXBox = kScanKB * 128;
-  constexpr uint32_t kOffS = 2 * kCBox, kOffX = kOffS + 2 * kSBox, kOffVec = kOffX + 4 * kXBox;
+  constexpr uint32_t kCBox = kScanRows * 128, kSBox = kScanP * 128;          // one 64-n box of C / of the state
+  constexpr uint32_t kCbTile = kScanRows * kScanU * 4, kXTile = kScanU * 128; // one unit: cb 16 KiB, x 4 KiB
+  constexpr uint32_t kSlot = kCbTile + kXTile;
+  constexpr uint32_t kOffS = 2 * kCBox, kOffRing = kOffS + 2 * kSBox, kOffVec = kOffRing + kScanSlots * kSlot;
   constexpr uint32_t kOffCtl = kOffVec + 2 * 256 * 4;
   float* dA_s = reinterpret_cast<float*>(smem + kOffVec);
   float* dt_s = dA_s + 256;
   const uint32_t bars = sbase + kOffCtl;
   const uint32_t bar_cs = bars, bar_acc = bars + 8;
-  auto bar_x = [&](int i) { return bars + 16 + 8u * i; };
-  auto bar_a_ready = [&](int i) { return bars + 48 + 8u * i; };
-  auto bar_a_free = [&](int i) { return bars + 64 + 8u * i; };
+  auto bar_full = [&](int i) { return bars + 16 + 8u * i; };
+  auto bar_free = [&](int i) { return bars + 40 + 8u * i; };
+  auto bar_a_ready = [&](int i) { return bars + 64 + 8u * i; };
   volatile int* ctl = reinterpret_cast<volatile int*>(smem + kOffCtl + 80);     // [0] abort, [1] tmem
   WaitCtx wc{ctl, a.status};
 
@@ -231,17 +238,31 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
   const int b = blockIdx.z / a.nchunks, c = blockIdx.z % a.nchunks;
   const int g = h / (a.nheads / a.ngroups);
   const int limit = min(L, a.seqlen - c * L);      // valid positions of this chunk
-  // 64-position blocks this tile needs: up to its own diagonal, and only those that hold data
-  const int nkb = min(2 * (mt + 1), (limit + kScanKB - 1) / kScanKB);
+  // units this tile needs: up to its own diagonal, and only those that hold data
+  const int nu = min((kScanRows / kScanU) * (mt + 1), (limit + kScanU - 1) / kScanU);
 
-  if (tid == 0) {
+  auto load_unit = [&](int u) {                     // service thread only
+    const int s = u % kScanSlots;
+    const uint32_t dst = sbase + kOffRing + s * kSlot;
+    mbar_expect_tx(bar_full(s), kSlot);
+    tma_load_5d(dst, &tmap_cb, bar_full(s), u * kScanU, mt * kScanRows, g, c, b);
+    tma_load_4d(dst + kCbTile, &tmap_x, bar_full(s), 0, h, c * L + u * kScanU, b);
+  };
+  if (warp == kScanRowWarps && lane == 0) {
     mbar_init(bar_cs, 1);
     mbar_init(bar_acc, 1);
-    for (int i = 0; i < 4; ++i) mbar_init(bar_x(i), 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_a_ready(i), kScanRowWarps); mbar_init(bar_a_free(i), 1); }
+    for (int i = 0; i < kScanSlots; ++i) { mbar_init(bar_full(i), 1); mbar_init(bar_free(i), 1); }
+    for (int i = 0; i < 2; ++i) mbar_init(bar_a_ready(i), kScanRowWarps);
     ctl[0] = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
+    // the first loads are on their way while the rest of the CTA sets up
+    mbar_expect_tx(bar_cs, 2 * kCBox + 2 * kSBox);
+    for (int kb = 0; kb < 2; ++kb) {
+      tma_load_4d(sbase + kb * kCBox, &tmap_C, bar_cs, kb * 64, g, c * L + mt * kScanRows, b);
+      tma_load_5d(sbase + kOffS + kb * kSBox, &tmap_S, bar_cs, kb * 64, 0, h, c, b);
+    }
+    for (int u = 0; u < nu && u < kScanSlots; ++u) load_unit(u);
   }
   if (warp == kScanRowWarps) {
     tmem_alloc(sbase + kOffCtl + 84, 256);
@@ -259,19 +280,10 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = static_cast<uint32_t>(ctl[1]);
-  constexpr uint32_t kAcc1 = 0, kAcc2 = 64, kA2 = 128;       // TMEM columns
+  constexpr uint32_t kAcc1 = 0, kAcc2 = 64, kA2 = 128;       // TMEM columns; two A2 slots of 16
 
   if (warp == kScanRowWarps) {
     if (lane == 0) {
-      mbar_expect_tx(bar_cs, 2 * kCBox + 2 * kSBox);
-      for (int kb = 0; kb < 2; ++kb) {
-        tma_load_4d(sbase + kb * kCBox, &tmap_C, bar_cs, kb * 64, g, c * L + mt * kScanRows, b);
-        tma_load_5d(sbase + kOffS + kb * kSBox, &tmap_S, bar_cs, kb * 64, 0, h, c, b);
-      }
-      for (int kb = 0; kb < nkb; ++kb) {
-        mbar_expect_tx(bar_x(kb), kXBox);
-        tma_load_4d(sbase + kOffX + kb * kXBox, &tmap_x, bar_x(kb), 0, h, c * L + kb * kScanKB, b);
-      }
       bool ok = mbar_wait(bar_cs, 0, wc, kScanWaitCS);
       if (ok) {
         tc_fence_after();
@@ -285,114 +297,136 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
         }
         // acc2 += A2 . x: A2 from tensor memory (K-major by construction), x MN-major as loaded
         const uint32_t idesc2 = mma_idesc(Pack16<T>::kFmt, false, true, kScanRows, kScanP);
-        for (int kb = 0; kb < nkb && ok; ++kb) {
-          ok = mbar_wait(bar_x(kb), 0, wc, kScanWaitX);
+        for (int u = 0; u < nu && ok; ++u) {
+          const int s = u % kScanSlots;
+          ok = mbar_wait(bar_full(s), (u / kScanSlots) & 1, wc, kScanWaitFull);
           if (!ok) break;
-          ok = mbar_wait(bar_a_ready(kb & 1), (kb >> 1) & 1, wc, kScanWaitAReady);
+          ok = mbar_wait(bar_a_ready(u & 1), (u >> 1) & 1, wc, kScanWaitAReady);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t bd0 = smem_desc_sw128(sbase + kOffX + kb * kXBox, kXBox, 1024);
-          for (int k16 = 0; k16 < kScanKB / 16; ++k16)
-            mma_f16_ts(tmem_base + kAcc2, tmem_base + kA2 + (kb & 1) * 32 + k16 * 8, bd0 + (uint64_t)((k16 * 2048) >> 4),
-                       idesc2, (kb | k16) != 0 ? 1u : 0u);
-          mma_commit(bar_a_free(kb & 1));
+          const uint64_t bd0 = smem_desc_sw128(sbase + kOffRing + s * kSlot + kCbTile, kXTile, 1024);
+          for (int k16 = 0; k16 < kScanU / 16; ++k16)
+            mma_f16_ts(tmem_base + kAcc2, tmem_base + kA2 + (u & 1) * 16 + k16 * 8, bd0 + (uint64_t)((k16 * 2048) >> 4),
+                       idesc2, (u | k16) != 0 ? 1u : 0u);
+          mma_commit(bar_free(s));
+          // refill the slot of the previous unit once its MMAs are complete
+          if (u >= 1 && u - 1 + kScanSlots < nu) {
+            const int ps = (u - 1) % kScanSlots;
+            ok = mbar_wait(bar_free(ps), ((u - 1) / kScanSlots) & 1, wc, kScanWaitFree);
+            if (!ok) break;
+            load_unit(u - 1 + kScanSlots);
+          }
         }
         if (ok) mma_commit(bar_acc);
       }
     }
   } else {
     const int r = (warp & 3) * 32 + lane;            // row of the tile = TMEM lane
-    const int half = warp >> 2;                      // which 32 positions of a block / which 32 headdim columns
+    const int half = warp >> 2;                      // which 16 positions of a unit / which 32 headdim columns
     const int m = mt * kScanRows + r;                // position inside the chunk
     const float am = dA_s[min(m, L - 1)];
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const float* cbrow = a.cb + (int64_t)b * a.cb_s[0] + (int64_t)c * a.cb_s[1] + (int64_t)g * a.cb_s[2] + (int64_t)m * a.cb_s[3];
+    // this thread's cb row inside a staged tile: 128 bytes, 16-byte pieces swizzled by row % 8
+    const uint32_t row_off = (uint32_t)r * 128;
+    const uint32_t rs = r & 7;
     bool ok = true;
-    for (int kb = 0; kb < nkb && ok; ++kb) {
-      ok = mbar_wait(bar_a_free(kb & 1), ((kb >> 1) & 1) ^ 1, wc, kScanWaitAFree);
+    for (int u = 0; u < nu && ok; ++u) {
+      const int s = u % kScanSlots;
+      const int k0 = u * kScanU + half * 16;
+      ok = mbar_wait(bar_full(s), (u / kScanSlots) & 1, wc, kScanWaitFull);
       if (!ok) break;
-      tc_fence_after();
-      {
-        const int k0 = kb * kScanKB + half * 32;
-        uint32_t o[16];
-        if (k0 > m) {                                // wholly above the diagonal
-#pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = 0u;
-        } else {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 t = __ldg(reinterpret_cast<const float4*>(cbrow + k0) + i);
-            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
-          }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int k = k0 + i;
-            float w = v[i] * fast_exp(fminf(am - dA_s[k], 0.0f));
-            w *= dt_s[k];
-            v[i] = (k <= m) ? w : 0.0f;
-          }
-#pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = PackPair<T>::pack(v[2 * i], v[2 * i + 1]);
-        }
-        tmem_st_32x32b_x16(tmem_base + lane_sel + kA2 + (kb & 1) * 32 + half * 16, o);
+      // the A2 slot is free once the MMAs of unit u - 2 are complete, which is what frees that unit's ring slot
+      if (u >= 2) {
+        ok = mbar_wait(bar_free((u - 2) % kScanSlots), ((u - 2) / kScanSlots) & 1, wc, kScanWaitFree);
+        if (!ok) break;
+        tc_fence_after();
       }
+      uint32_t o[8];
+      if (k0 > m) {                                  // wholly above the diagonal
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = 0u;
+      } else {
+        const uint8_t* tile = smem + kOffRing + s * kSlot + row_off;
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 t = *reinterpret_cast<const float4*>(tile + (((half * 4 + i) ^ rs) << 4));
+          v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+        float ak[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 t = *reinterpret_cast<const float4*>(dA_s + k0 + 4 * i);
+          const float4 d = *reinterpret_cast<const float4*>(dt_s + k0 + 4 * i);
+          ak[4 * i] = t.x; ak[4 * i + 1] = t.y; ak[4 * i + 2] = t.z; ak[4 * i + 3] = t.w;
+          dk[4 * i] = d.x; dk[4 * i + 1] = d.y; dk[4 * i + 2] = d.z; dk[4 * i + 3] = d.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = v[i] * fast_exp(fminf(am - ak[i], 0.0f)) * dk[i];
+        if (k0 + 15 > m) {                           // the diagonal runs through this piece
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (k0 + i > m) v[i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = PackPair<T>::pack(v[2 * i], v[2 * i + 1]);
+      }
+      tmem_st_32x32b_x8(tmem_base + lane_sel + kA2 + (u & 1) * 16 + half * 8, o);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_a_ready(kb & 1));
+      if (lane == 0) mbar_arrive(bar_a_ready(u & 1));
     }
     // ---- epilogue: out = exp(a_m) * acc1 + acc2 + D * x[m]
-    if (ok) ok = mbar_wait(bar_acc, 0, wc, kScanWaitAcc, 64);
     const bool live = m < limit;
-    // the x block that holds position m is read below with ordinary loads: observe its barrier
-    if (ok && live && a.D != nullptr) ok = mbar_wait(bar_x(m / kScanKB), 0, wc, kScanWaitX);
+    const int q = half;
+    const int64_t pos = (int64_t)c * L + m;
+    const uint8_t* xrow = static_cast<const uint8_t*>(a.x) +
+                          2 * ((int64_t)b * a.x_s[0] + pos * a.x_s[1] + (int64_t)h * a.x_s[2]) + q * 64;
+    uint4 xr[4];
+    if (a.D != nullptr && live) {                    // requested before the wait, used after it
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) xr[pc] = __ldg(reinterpret_cast<const uint4*>(xrow) + pc);
+    }
+    const float dh = (a.D != nullptr && !a.D_has_hdim) ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride) : 0.0f;
+    if (ok) ok = mbar_wait(bar_acc, 0, wc, kScanWaitAcc, 64);
     if (ok) {
       tc_fence_after();
       const float sm = fast_exp(am);
-      const float dh = (a.D != nullptr && !a.D_has_hdim) ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride) : 0.0f;
-      // x[m, :] sits in the x block that holds position m: row m % 64, 16-byte pieces swizzled by row % 8
-      const uint8_t* xrow = smem + kOffX + (m / kScanKB) * kXBox + (m % kScanKB) * 128;
-      const int xs = m & 7;
       uint8_t* orow = static_cast<uint8_t*>(a.out) +
-                      2 * ((int64_t)b * a.out_s[0] + (int64_t)(c * L + m) * a.out_s[1] + (int64_t)h * a.out_s[2]);
-      {
-        const int q = half;
-        uint32_t r1[32], r2[32];
-        tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
-        tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
-        tmem_ld_wait();
-        float res[32];
+                      2 * ((int64_t)b * a.out_s[0] + pos * a.out_s[1] + (int64_t)h * a.out_s[2]) + q * 64;
+      uint32_t r1[32], r2[32];
+      tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
+      tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
+      tmem_ld_wait();
+      float res[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) res[i] = fmaf(__uint_as_float(r1[i]), sm, 0.0f) + __uint_as_float(r2[i]);
-        if (a.D != nullptr && live) {
+      for (int i = 0; i < 32; ++i) res[i] = __uint_as_float(r1[i]) * sm + __uint_as_float(r2[i]);
+      if (a.D != nullptr && live) {
 #pragma unroll
-          for (int pc = 0; pc < 4; ++pc) {           // 16-byte pieces = 8 headdim columns
-            const int piece = q * 4 + pc;
-            const uint4 t = *reinterpret_cast<const uint4*>(xrow + ((piece ^ xs) << 4));
-            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+        for (int pc = 0; pc < 4; ++pc) {             // 16-byte pieces = 8 headdim columns
+          const uint32_t w[4] = {xr[pc].x, xr[pc].y, xr[pc].z, xr[pc].w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float x0, x1;
-              PackPair<T>::unpack(w[i], x0, x1);
-              const int pcol = piece * 8 + 2 * i;
-              const float d0 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol) : dh;
-              const float d1 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol + 1) : dh;
-              res[pc * 8 + 2 * i] += x0 * d0;
-              res[pc * 8 + 2 * i + 1] += x1 * d1;
-            }
+          for (int i = 0; i < 4; ++i) {
+            float x0, x1;
+            PackPair<T>::unpack(w[i], x0, x1);
+            const int pcol = q * 32 + pc * 8 + 2 * i;
+            const float d0 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol) : dh;
+            const float d1 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol + 1) : dh;
+            res[pc * 8 + 2 * i] += x0 * d0;
+            res[pc * 8 + 2 * i + 1] += x1 * d1;
           }
         }
-        if (live) {
+      }
+      if (live) {
 #pragma unroll
-          for (int pc = 0; pc < 4; ++pc) {
-            uint4 t;
-            t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
-            t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
-            t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
-            t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
-            *reinterpret_cast<uint4*>(orow + (q * 4 + pc) * 16) = t;
-          }
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 t;
+          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
+          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
+          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
+          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
+          *reinterpret_cast<uint4*>(orow + pc * 16) = t;
         }
       }
     }
@@ -492,36 +526,42 @@ int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream
   const int L = p.chunk_size;
   const int nchunks = (p.seqlen + L - 1) / L;
   SSD_REQUIRE((long long)p.batch * nchunks <= 65535, SSD_ERR_UNSUPPORTED, "chunk scan grid too large");
-  CUtensorMap mC, mS, mx;
+  CUtensorMap mC, mS, mx, mcb;
   int rc = make_rows_map(&mC, p.C, p.in_dtype, p.dstate, p.ngroups, p.seqlen, p.batch, p.C_stride, kScanRows);
   if (rc != SSD_OK) return rc;
-  rc = make_rows_map(&mx, p.x, p.in_dtype, p.headdim, p.nheads, p.seqlen, p.batch, p.x_stride, kScanKB);
+  rc = make_rows_map(&mx, p.x, p.in_dtype, p.headdim, p.nheads, p.seqlen, p.batch, p.x_stride, kScanU);
+  if (rc != SSD_OK) return rc;
+  rc = make_cb_map(&mcb, p.cb, L, p.ngroups, nchunks, p.batch, p.cb_stride, kScanU, kScanRows);
   if (rc != SSD_OK) return rc;
   rc = make_states_map(&mS, p.states, p.in_dtype, p.nheads, nchunks, p.batch, p.states_stride);
   if (rc != SSD_OK) return rc;
   ScanArgs a{};
-  a.cb = static_cast<const float*>(p.cb);
+  a.x = p.x;
   a.dt = p.dt;
   a.dA = p.dA_cumsum;
   a.D = p.D;
   a.out = p.out;
   SSD_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&a.status), g_scan_status));
-  for (int i = 0; i < 4; ++i) a.cb_s[i] = p.cb_stride[i];
-  for (int i = 0; i < 3; ++i) { a.dt_s[i] = p.dt_stride[i]; a.dA_s[i] = p.dA_stride[i]; a.out_s[i] = p.out_stride[i]; }
+  for (int i = 0; i < 3; ++i) {
+    a.dt_s[i] = p.dt_stride[i];
+    a.dA_s[i] = p.dA_stride[i];
+    a.out_s[i] = p.out_stride[i];
+    a.x_s[i] = p.x_stride[i];
+  }
   a.D_stride = p.D_stride;
   a.D_dtype = p.D_dtype;
   a.D_has_hdim = p.D_has_hdim;
-  a.out_dtype = p.in_dtype;
   a.L = L;
   a.seqlen = p.seqlen;
   a.nheads = p.nheads;
   a.ngroups = p.ngroups;
   a.nchunks = nchunks;
-  const int smem = 2 * kScanRows * 128 + 2 * kScanP * 128 + 4 * kScanKB * 128 + 2 * 256 * 4 + 128 + 1024;
+  const int smem = 2 * kScanRows * 128 + 2 * kScanP * 128 + kScanSlots * (kScanRows * kScanU * 4 + kScanU * 128) +
+                   2 * 256 * 4 + 128 + 1024;
   auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_kernel<__nv_bfloat16> : chunk_scan_kernel<__half>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
-  kern<<<grid, kScanThreads, smem, stream>>>(mC, mS, mx, a);
+  kern<<<grid, kScanThreads, smem, stream>>>(mC, mS, mx, mcb, a);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }

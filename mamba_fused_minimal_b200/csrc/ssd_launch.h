@@ -42,6 +42,11 @@ int make_rows_map(CUtensorMap* map, const void* base, int dtype, int inner, int 
 int make_states_map(CUtensorMap* map, const void* base, int dtype, int nheads, int nchunks, int batch,
                     const int64_t* stride);
 
+// 5-D tensor map over the fp32 chunk products cb (b, c, g, m, k) with k contiguous (strides in
+// elements: b, c, g, m); box = box_k columns x box_m rows, 128-byte swizzle (box_k * 4 <= 128).
+int make_cb_map(CUtensorMap* map, const void* base, int L, int ngroups, int nchunks, int batch, const int64_t* stride,
+                int box_k, int box_m);
+
 // ---- tcgen05 chunk bmm and chunk scan (ssd_gemm_sm100.cu) -----------------------------
 int bmm_fast_ok(const ssd_bmm_chunk_params_t& p);
 int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream);
