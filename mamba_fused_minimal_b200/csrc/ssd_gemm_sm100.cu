@@ -195,9 +195,11 @@ struct ScanArgs {
   const float* dt;
   const float* dA;
   const void* D;
+  const void* z;                       // gate, same layout rules as x; NULL: no gating
   void* out;
+  void* out_x;                         // the ungated result when z is given (strides of out)
   int* status;
-  int64_t x_s[3];                      // b, l, h (p stride is 1)
+  int64_t x_s[3], z_s[3];              // b, l, h (p stride is 1)
   int64_t dt_s[3], dA_s[3];            // b, h, c (L stride is 1)
   int64_t out_s[3];                    // b, l, h (p stride is 1)
   int64_t D_stride;
@@ -388,6 +390,13 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
 #pragma unroll
       for (int pc = 0; pc < 4; ++pc) xr[pc] = __ldg(reinterpret_cast<const uint4*>(xrow) + pc);
     }
+    uint4 zr[4];
+    if (a.z != nullptr && live) {
+      const uint8_t* zrow = static_cast<const uint8_t*>(a.z) +
+                            2 * ((int64_t)b * a.z_s[0] + pos * a.z_s[1] + (int64_t)h * a.z_s[2]) + q * 64;
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) zr[pc] = __ldg(reinterpret_cast<const uint4*>(zrow) + pc);
+    }
     const float dh = (a.D != nullptr && !a.D_has_hdim) ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride) : 0.0f;
     if (ok) ok = mbar_wait(bar_acc, 0, wc, kScanWaitAcc, 64);
     if (ok) {
@@ -415,6 +424,28 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
             const float d1 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol + 1) : dh;
             res[pc * 8 + 2 * i] += x0 * d0;
             res[pc * 8 + 2 * i + 1] += x1 * d1;
+          }
+        }
+      }
+      if (a.z != nullptr && live) {
+        // out_x = the ungated result; out = out_x * z * sigmoid(z)   (ssd_chunk_scan.py device code)
+        uint8_t* oxrow = static_cast<uint8_t*>(a.out_x) +
+                         2 * ((int64_t)b * a.out_s[0] + pos * a.out_s[1] + (int64_t)h * a.out_s[2]) + q * 64;
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 t;
+          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
+          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
+          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
+          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
+          *reinterpret_cast<uint4*>(oxrow + pc * 16) = t;
+          const uint32_t w[4] = {zr[pc].x, zr[pc].y, zr[pc].z, zr[pc].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float z0, z1;
+            PackPair<T>::unpack(w[i], z0, z1);
+            res[pc * 8 + 2 * i] *= z0 * (1.0f / (1.0f + expf(-z0)));
+            res[pc * 8 + 2 * i + 1] *= z1 * (1.0f / (1.0f + expf(-z1)));
           }
         }
       }
@@ -503,7 +534,14 @@ int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream) 
 int scan_fast_ok(const ssd_chunk_scan_params_t& p) {
   if (p.in_dtype != SSD_BF16 && p.in_dtype != SSD_F16) return 0;
   if (p.states_dtype != p.in_dtype || p.cb_dtype != SSD_F32) return 0;
-  if (p.z != nullptr || p.seq_idx != nullptr) return 0;
+  if (p.seq_idx != nullptr) return 0;
+  if (p.z != nullptr) {
+    if (p.out_x == nullptr || p.z_stride[3] != 1 || (reinterpret_cast<uintptr_t>(p.z) & 15) ||
+        (reinterpret_cast<uintptr_t>(p.out_x) & 15))
+      return 0;
+    for (int i = 0; i < 3; ++i)
+      if (p.z_stride[i] % 8 != 0) return 0;
+  }
   if (p.headdim != kScanP || p.dstate != kScanN) return 0;
   if (p.chunk_size != 128 && p.chunk_size != 256) return 0;
   if (p.x_stride[3] != 1 || p.C_stride[3] != 1 || p.states_stride[4] != 1 || p.out_stride[3] != 1 || p.cb_stride[4] != 1 ||
@@ -537,6 +575,8 @@ int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream
   if (rc != SSD_OK) return rc;
   ScanArgs a{};
   a.x = p.x;
+  a.z = p.z;
+  a.out_x = p.out_x;
   a.dt = p.dt;
   a.dA = p.dA_cumsum;
   a.D = p.D;
@@ -547,6 +587,7 @@ int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream
     a.dA_s[i] = p.dA_stride[i];
     a.out_s[i] = p.out_stride[i];
     a.x_s[i] = p.x_stride[i];
+    a.z_s[i] = p.z_stride[i];
   }
   a.D_stride = p.D_stride;
   a.D_dtype = p.D_dtype;

@@ -37,6 +37,19 @@ def test_chunk_scan_against_oracle(cuda_device, dtype, b, l, h, g, L, d_hdim, wi
     assert torch.isfinite(out).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_chunk_scan_with_gate(cuda_device, dtype):
+    """z gating: out_x is the ungated result, out = out_x * z * sigmoid(z)."""
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _chunk_scan_fwd
+    inp, d, dA, dt, passed, cb, D = _case(cuda_device, dtype, 2, 700, 4, 2, 256, seed=11)
+    z = torch.randn(2, 700, 4, 64, generator=torch.Generator().manual_seed(12)).to(dtype)
+    out, out_x = _chunk_scan_fwd(cb, d["x"], dt, dA, d["C"], passed, D=D.to(cuda_device), z=z.to(cuda_device))
+    ref, ref_x = O.chunk_scan_fwd(cb.cpu(), inp["x"], dt.cpu(), dA.cpu(), inp["C"], passed.cpu(), D=D, z=z, exp_impl="ex2")
+    for got, want in ((out, ref), (out_x, ref_x)):
+        scale = want.float().abs().max()
+        torch.testing.assert_close(got.float().cpu() / scale, want.float() / scale, atol=1e-2, rtol=1e-2)
+
+
 def test_chunk_scan_fast_and_plain_kernels_agree(cuda_device):
     """The same data through the tcgen05 kernel and, forced by an all-zero seq_idx (one
     sequence, no boundary), through the plain kernel."""
