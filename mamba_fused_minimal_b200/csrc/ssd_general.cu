@@ -270,11 +270,90 @@ state_passing_kernel(ssd_state_passing_params_t p) {
                  (int64_t)d * p.final_stride[2]] = s;
 }
 
+// The same recurrence with four consecutive state elements per thread (16-byte fp32 / 8-byte
+// 16-bit accesses through the Quad helpers of the carry kernels) and the loads of kSpAhead chunks
+// in flight: the kernel is a pure stream (read every chunk state once, write every passed
+// state once), so what matters is memory-level parallelism.  Needs dim-contiguous, aligned
+// tensors; launch_state_passing falls back to the kernel above otherwise.
+constexpr int kSpAhead = 4;
+
+template <typename ST, typename OT>
+__global__ void __launch_bounds__(256)
+state_passing_vec_kernel(ssd_state_passing_params_t p) {
+  const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  if (d >= p.dim) return;
+  float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (p.initial_states != nullptr) {
+    const int64_t ib = (int64_t)b * p.init_stride[0] + (int64_t)h * p.init_stride[1] + d;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[e] = load_f(p.initial_states, p.init_dtype, ib + e);
+  }
+  const ST* src = static_cast<const ST*>(p.states) + (int64_t)b * p.states_stride[0] + (int64_t)h * p.states_stride[2] + d;
+  OT* dst = static_cast<OT*>(p.out) + (int64_t)b * p.out_stride[0] + (int64_t)h * p.out_stride[2] + d;
+  const int64_t abase = (int64_t)b * p.dA_stride[0] + (int64_t)h * p.dA_stride[1];
+  int seq_prev = 0;
+  for (int c0 = 0; c0 < p.nchunks; c0 += kSpAhead) {
+    float cur[kSpAhead][4], scale[kSpAhead];
+#pragma unroll
+    for (int u = 0; u < kSpAhead; ++u) {
+      const int c = c0 + u;
+      if (c < p.nchunks) {
+        Quad<ST, true>::load(src + (int64_t)c * p.states_stride[1], 4, cur[u]);
+        scale[u] = fast_exp(load_f(p.dA_chunk_cumsum, p.dA_dtype, abase + (int64_t)c * p.dA_stride[2]));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kSpAhead; ++u) {
+      const int c = c0 + u;
+      if (c < p.nchunks) {
+        Quad<OT, true>::store(dst + (int64_t)c * p.out_stride[1], 4, s);
+        float sc = scale[u];
+        if (p.seq_idx != nullptr) {
+          const int pos = min((c + 1) * p.chunk_size, p.seqlen) - 1;
+          const int seq_new = p.seq_idx[(int64_t)b * p.seq_idx_stride[0] + (int64_t)pos * p.seq_idx_stride[1]];
+          if (seq_new != seq_prev) sc = 0.0f;
+          seq_prev = seq_new;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] = fmaf(sc, s[e], cur[u][e]);
+      }
+    }
+  }
+  float* fo = p.final_states + (int64_t)b * p.final_stride[0] + (int64_t)h * p.final_stride[1] + d;
+  *reinterpret_cast<float4*>(fo) = make_float4(s[0], s[1], s[2], s[3]);
+}
+
+template <typename ST>
+void launch_state_passing_vec(const ssd_state_passing_params_t& p, dim3 grid, cudaStream_t stream) {
+  switch (p.out_dtype) {
+    case SSD_BF16: state_passing_vec_kernel<ST, __nv_bfloat16><<<grid, 256, 0, stream>>>(p); break;
+    case SSD_F16: state_passing_vec_kernel<ST, __half><<<grid, 256, 0, stream>>>(p); break;
+    default: state_passing_vec_kernel<ST, float><<<grid, 256, 0, stream>>>(p); break;
+  }
+}
+
 int launch_state_passing(const ssd_state_passing_params_t& p, cudaStream_t stream) {
   SSD_REQUIRE(p.nheads <= 65535 && p.batch <= 65535, SSD_ERR_UNSUPPORTED,
               "state passing grid too large (nheads %d, batch %d)", p.nheads, p.batch);
-  dim3 grid((p.dim + 255) / 256, p.nheads, p.batch);
-  state_passing_kernel<<<grid, 256, 0, stream>>>(p);
+  auto aligned = [](const void* q, int dtype) { return (reinterpret_cast<uintptr_t>(q) % (4 * dtype_size(dtype))) == 0; };
+  bool vec = p.dim % 4 == 0 && p.states_stride[3] == 1 && p.out_stride[3] == 1 && p.final_stride[2] == 1 &&
+             aligned(p.states, p.states_dtype) && aligned(p.out, p.out_dtype) && aligned(p.final_states, SSD_F32) &&
+             (p.initial_states == nullptr || p.init_stride[2] == 1);
+  for (int i = 0; i < 3; ++i) vec = vec && p.states_stride[i] % 4 == 0 && p.out_stride[i] % 4 == 0;
+  for (int i = 0; i < 2; ++i) vec = vec && p.final_stride[i] % 4 == 0;
+  if (vec) {
+    dim3 grid((p.dim / 4 + 255) / 256, p.nheads, p.batch);
+    switch (p.states_dtype) {
+      case SSD_BF16: launch_state_passing_vec<__nv_bfloat16>(p, grid, stream); break;
+      case SSD_F16: launch_state_passing_vec<__half>(p, grid, stream); break;
+      default: launch_state_passing_vec<float>(p, grid, stream); break;
+    }
+  } else {
+    dim3 grid((p.dim + 255) / 256, p.nheads, p.batch);
+    state_passing_kernel<<<grid, 256, 0, stream>>>(p);
+  }
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }
