@@ -132,6 +132,7 @@ struct FusedArgs {
   const float* dt;
   const float* dA;
   const void* init;
+  const int32_t* seq_idx; // (b, l) sequence index of each position, or NULL
   void* out;
   float* final_states;
   void* states;
@@ -139,7 +140,7 @@ struct FusedArgs {
   uint32_t* flags;        // [cta][HPC]
   float* carry;           // [cta][HPC][kP * kN]
   int64_t dt_s[3], dA_s[3];                 // b, h, c strides (elements); L stride is 1
-  int64_t init_s[3], out_s[4], final_s[3], states_s[4];
+  int64_t init_s[3], out_s[4], final_s[3], states_s[4], seq_s[2];
   int batch, seqlen, nheads, ngroups, chunk_size, nchunks;
   int strips_per_batch;   // nheads / HPC
   int init_dtype, out_dtype, states_dtype;
@@ -207,7 +208,7 @@ template <> struct Pack<__half> {
   }
 };
 
-template <typename T, int HPC, bool OUT32>
+template <typename T, int HPC, bool OUT32, bool SEQ>
 __global__ void __launch_bounds__(Cfg<HPC>::THREADS, 1)
 fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_B,
                    const __grid_constant__ CUtensorMap tmap_out, const FusedArgs a) {
@@ -394,6 +395,15 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           }
           const float* dd = reinterpret_cast<const float*>(smem + C::OFF_DTDA + r * C::DTDA_SLOT);
           float* sc = reinterpret_cast<float*>(smem + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT);
+          // packed sequences: a position contributes to the chunk's state only if it belongs to
+          // the same sequence as the chunk's last position (kernels/ssd_chunk_state.py:147-152)
+          const int limit = min(L, a.seqlen - c * L);
+          const int32_t* sq = nullptr;
+          int seq_last = 0;
+          if constexpr (SEQ) {
+            sq = a.seq_idx + (int64_t)(strip / a.strips_per_batch) * a.seq_s[0] + (int64_t)c * L * a.seq_s[1];
+            seq_last = sq[(int64_t)(limit - 1) * a.seq_s[1]];
+          }
 #pragma unroll
           for (int hd = 0; hd < HPC; ++hd) {
             const float* row = dd + hd * 2 * kMaxL;
@@ -401,7 +411,11 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             for (int k = lane; k < L; k += 32) {
               float d = last - row[kMaxL + k];
               if (a.clamp_decay) d = fminf(d, 0.0f);
-              sc[hd * kMaxL + k] = fast_exp(d) * row[k];
+              float f = fast_exp(d) * row[k];
+              if constexpr (SEQ) {
+                if (k < limit && sq[(int64_t)k * a.seq_s[1]] != seq_last) f = 0.0f;
+              }
+              sc[hd * kMaxL + k] = f;
             }
           }
           __syncwarp();                       // every lane has read the rows and written its factors
@@ -596,11 +610,25 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           for (int i = 0; i < kP; ++i) S[i] = __ldcg(cin + fp(i) * kN + fn(i));
         }
       }
+      // packed sequences: the running state is dropped where the sequence changes between the
+      // ends of two successive chunks (kernels/ssd_state_passing.py:66-76)
+      const int32_t* sq = nullptr;
+      int seq_prev = 0;
+      if constexpr (SEQ) {
+        sq = a.seq_idx + (int64_t)b * a.seq_s[0];
+        if (c0 > 0) seq_prev = sq[(int64_t)(c0 * L - 1) * a.seq_s[1]];
+      }
       for (int c = c0; c < c1 && ok; ++c, ++item) {
         const int buf = item % C::NBUF;
         float decay = 0.0f;
-        if (a.mode == 0)
+        if (a.mode == 0) {
           decay = fast_exp(__ldg(a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2] + (L - 1)));
+          if constexpr (SEQ) {
+            const int seq_new = sq[(int64_t)(min((c + 1) * L, a.seqlen) - 1) * a.seq_s[1]];
+            if (seq_new != seq_prev) decay = 0.0f;
+            seq_prev = seq_new;
+          }
+        }
         ok = mbar_wait(bar_acc_full(hd, buf), (item / C::NBUF) & 1, wc, kWaitAccFull, 128);
         if (!ok) break;
         tc_fence_after();
@@ -836,6 +864,9 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   a.dt = in.dt;
   a.dA = in.dA_cumsum;
   a.init = p.initial_states;
+  a.seq_idx = in.seq_idx;
+  a.seq_s[0] = in.seq_idx_stride[0];
+  a.seq_s[1] = in.seq_idx_stride[1];
   a.out = p.out;
   a.final_states = p.final_states;
   a.states = p.states;
@@ -875,14 +906,18 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
 
   const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
   int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
-  auto kern = (p.out_dtype == SSD_F32 && mode == 0) ? fused_state_kernel<T, HPC, true> : fused_state_kernel<T, HPC, false>;
+  const bool out32 = p.out_dtype == SSD_F32 && mode == 0;
+  const bool seq = in.seq_idx != nullptr;
+  auto kern = out32 ? (seq ? fused_state_kernel<T, HPC, true, true> : fused_state_kernel<T, HPC, true, false>)
+                    : (seq ? fused_state_kernel<T, HPC, false, true> : fused_state_kernel<T, HPC, false, false>);
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   // A strip longer than a CTA's range would make the CTAs of that strip wait for one another
   // in turn; then the carry is deferred to a second, small kernel instead.
   // (Only when the ranges are long: for short ones the chained carry costs next to nothing and
   // keeps the passed states free of the second rounding that a later correction implies.)
   const long long per_cta = (total + grid - 1) / grid;
-  a.defer = (mode == 0 && a.nchunks > per_cta && per_cta >= 16) ? 1 : 0;
+  // (not with packed sequences: the second pass multiplies decays across a cut and knows nothing of resets)
+  a.defer = (mode == 0 && a.nchunks > per_cta && per_cta >= 16 && in.seq_idx == nullptr) ? 1 : 0;
   kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(mx, mB, mo, a);
   SSD_CUDA_OK(cudaGetLastError());
   if (a.defer) {
@@ -967,7 +1002,6 @@ int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why) {
   if (in.in_dtype != SSD_BF16 && in.in_dtype != SSD_F16) return no("inputs are not bf16/fp16");
   if (in.headdim != kP || in.dstate != kN) return no("headdim != 64 or dstate != 128");
   if (in.chunk_size % kKT != 0 || in.chunk_size > kMaxL) return no("chunk_size not a multiple of 64 up to 256");
-  if (in.seq_idx != nullptr) return no("seq_idx given");
   if (in.x_stride[3] != 1 || in.B_stride[3] != 1) return no("x or B innermost stride != 1");
   if (!aligned16(in.x) || !aligned16(in.B)) return no("x or B not 16-byte aligned");
   for (int i = 0; i < 3; ++i)

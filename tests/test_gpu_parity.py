@@ -289,6 +289,43 @@ def test_seq_idx_plain_kernels(cuda_device):
     assert_close16(y, ref_y, "y")
 
 
+@pytest.mark.parametrize("h,g,L", [(4, 1, 128), (3, 3, 64), (8, 2, 256)])
+def test_seq_idx_tcgen05_state_path(cuda_device, h, g, L):
+    """Packed sequences on the shapes the tcgen05 state kernel takes (headdim 64, dstate 128,
+    16-bit inputs): boundaries inside a chunk, on a chunk edge, and a ragged last chunk; both
+    the fused entry point and the per-chunk states alone."""
+    S = _shims()
+    b, l = 2, 5 * L + 37
+    inp = O.make_inputs(b, l, h, 64, g, 128, dtype=torch.bfloat16, seed=29 + h)
+    seq_idx = torch.zeros(b, l, dtype=torch.int32)
+    seq_idx[:, L + 5:] = 1
+    seq_idx[:, 3 * L:] = 2            # on a chunk edge
+    seq_idx[1, 4 * L + 9:] = 3        # only in the second batch element
+    seq_idx[:, 5 * L + 20:] = 4       # inside the ragged last chunk
+    d = _dev(inp, cuda_device)
+    si = seq_idx.to(cuda_device)
+    dA, dt = S["cumsum"](d["dt"], d["A"], L, dt_bias=d["dt_bias"], dt_softplus=True)
+    init = torch.randn(b, h, 64, 128, generator=torch.Generator().manual_seed(5))
+    out, fin = S["fused_c"](d["B"], d["x"], dt, dA, torch.bfloat16, initial_states=init.to(cuda_device), seq_idx=si)
+    ref_out, ref_fin = O.fused_state_fwd(inp["B"], inp["x"], dt.cpu(), dA.cpu(), torch.bfloat16, initial_states=init,
+                                         seq_idx=seq_idx, exp_impl="ex2")
+    assert_close16(out, ref_out, "passed states")
+    assert_close32(fin, ref_fin, "final states")
+    st = S["chunk_state"](d["B"], d["x"], dt, dA, seq_idx=si)
+    ref_st = O.chunk_state_fwd(inp["B"], inp["x"], dt.cpu(), dA.cpu(), seq_idx=seq_idx, exp_impl="ex2")
+    assert_close32(st, ref_st, "chunk states")
+    # and the plain kernels on the same data
+    out_p, fin_p = _fused_general(S, d, dt, dA, init.to(cuda_device), si)
+    assert_close16(out, out_p.float().cpu(), "fast vs plain passed states")
+    assert_close32(fin, fin_p.cpu(), "fast vs plain final states")
+
+
+def _fused_general(S, d, dt, dA, init, si):
+    from mamba_fused_minimal_b200.kernels._fused import _fused_chunk_state_state_passing_fwd
+    return _fused_chunk_state_state_passing_fwd(d["B"], d["x"], dt, dA, torch.bfloat16, initial_states=init, seq_idx=si,
+                                                force_general=True)
+
+
 def test_headline_shape_properties(cuda_device):
     """Mamba2-2.7B layer shape in full (batch 8 x 4096 x 80 heads): the oracle on a slice
     (one batch element, four heads) plus size-independent properties on the whole result."""
