@@ -361,3 +361,33 @@ def test_headline_shape_properties(cuda_device):
     assert_close32(nxt - decay * o32, st, "recurrence identity", tol=1e-4)
     from mamba_fused_minimal_b200._ext import C
     C.check_status(d["x"])
+
+
+def test_largest_shape_against_plain_kernels_on_a_slice(cuda_device):
+    """The largest configuration (batch 16 x 8192, 128 heads in 8 groups): the tcgen05 kernels on the
+    whole problem against the plain kernels on one batch element and one group (offsets past 2^31
+    bytes, grids of thousands of tiles)."""
+    from mamba_fused_minimal_b200.kernels._fused import _fused_chunk_state_state_passing_fwd
+    from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
+    S = _shims()
+    b, l, h, g, L = 16, 8192, 128, 8, 256
+    d = generate_benchmark_data(b, l, h, 64, g, 128, device=cuda_device, seed=3)
+    C = torch.randn_like(d["B"])
+    dA, dt = S["cumsum"](d["dt"], d["A"], L, dt_bias=d["dt_bias"], dt_softplus=True)
+    out, fin = S["fused_c"](d["B"], d["x"], dt, dA, torch.bfloat16)
+    cb = S["bmm"](C, d["B"], L, output_dtype=torch.float32)
+    Dv = torch.randn(h, device=cuda_device)
+    y, _ = S["chunk_scan"](cb, d["x"], dt, dA, C, out, D=Dv)
+    # slice: last batch element, last group (the far end of every tensor)
+    bs, gs = b - 1, g - 1
+    hs = slice(gs * (h // g), (gs + 1) * (h // g))
+    xs, Bs, Cs = d["x"][bs:, :, hs].contiguous(), d["B"][bs:, :, gs:].contiguous(), C[bs:, :, gs:].contiguous()
+    dts, dAs = dt[bs:, hs].contiguous(), dA[bs:, hs].contiguous()
+    out_p, fin_p = _fused_chunk_state_state_passing_fwd(Bs, xs, dts, dAs, torch.bfloat16, force_general=True)
+    assert_close16(out[bs:, :, hs], out_p.float().cpu(), "passed states")
+    assert_close32(fin[bs:, hs], fin_p.cpu(), "final states")
+    si = torch.zeros(1, l, dtype=torch.int32, device=cuda_device)      # routes to the plain kernels
+    cb_p = S["bmm"](Cs, Bs, L, seq_idx=si, output_dtype=torch.float32)
+    assert_close32(cb[bs:, :, gs:], cb_p.cpu(), "CB", tol=1e-5)
+    y_p, _ = S["chunk_scan"](cb_p, xs, dts, dAs, Cs, out[bs:, :, hs].contiguous(), D=Dv[hs], seq_idx=si)
+    assert_close16(y[bs:, :, hs], y_p.float().cpu(), "out")
