@@ -74,6 +74,12 @@ __device__ __forceinline__ float fast_exp(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
   return y;
 }
+// 2^y with the same instruction, for callers that have already multiplied by log2 e.
+__device__ __forceinline__ float ex2_approx(float y) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(y));
+  return r;
+}
 
 // log(exp(x) + 1) where x <= 20, x otherwise: the reference's softplus
 // (kernels/softplus.py:8-10 applied at kernels/ssd_chunk_state.py:70).  exp as everywhere in

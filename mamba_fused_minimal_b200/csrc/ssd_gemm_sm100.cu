@@ -363,8 +363,20 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
           ak[4 * i] = t.x; ak[4 * i + 1] = t.y; ak[4 * i + 2] = t.z; ak[4 * i + 3] = t.w;
           dk[4 * i] = d.x; dk[4 * i + 1] = d.y; dk[4 * i + 2] = d.z; dk[4 * i + 3] = d.w;
         }
+        // two positions per instruction (packed fp32): the same IEEE operations in the same order
+        // as cb * exp(min(a_m - a_k, 0)) * dt_k one element at a time
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = v[i] * fast_exp(fminf(am - ak[i], 0.0f)) * dk[i];
+        for (int i = 0; i < 16; i += 2) {
+          float2 dl = __ffma2_rn(make_float2(ak[i], ak[i + 1]), make_float2(-1.0f, -1.0f), make_float2(am, am));
+          dl.x = fminf(dl.x, 0.0f);
+          dl.y = fminf(dl.y, 0.0f);
+          dl = __fmul2_rn(dl, make_float2(1.4426950408889634f, 1.4426950408889634f));
+          const float2 e = make_float2(ex2_approx(dl.x), ex2_approx(dl.y));
+          float2 w = __fmul2_rn(make_float2(v[i], v[i + 1]), e);
+          w = __fmul2_rn(w, make_float2(dk[i], dk[i + 1]));
+          v[i] = w.x;
+          v[i + 1] = w.y;
+        }
         if (k0 + 15 > m) {                           // the diagonal runs through this piece
 #pragma unroll
           for (int i = 0; i < 16; ++i)
