@@ -160,10 +160,14 @@ SSD_API int ssd_state_passing_fwd(const ssd_state_passing_params_t* prm, ssd_str
  *    that gives up sets a status word (see ssd_check_status).
  *
  *    `workspace`: ssd_fused_state_workspace_bytes() bytes, 256-byte aligned, owned by the
- *    caller, used by one call at a time.  Its first 1 KiB must be zero on the first use
- *    and is left zero-equivalent by every call (flags carry an epoch), so one buffer can
- *    be reused by successive calls on the same stream without clearing.
+ *    caller, used by one call at a time.  Its first SSD_FUSED_WORKSPACE_HEADER_BYTES
+ *    (4096: status word, launch epoch, done counter and one flag word per CTA and head
+ *    slot) must be zero on the first use -- zeroing the whole buffer once is the simple
+ *    way -- and are left zero-equivalent by every call (flags carry an epoch), so one
+ *    buffer can be reused by successive calls on the same stream without clearing.  After
+ *    SSD_ERR_TIMEOUT from ssd_check_status the same bytes must be cleared again.
  * ---------------------------------------------------------------------------------- */
+#define SSD_FUSED_WORKSPACE_HEADER_BYTES 4096
 typedef struct {
   ssd_state_inputs_t in;
   const void* initial_states; /* (b, h, p, n) of init_dtype, (p, n) contiguous, or NULL */
@@ -187,13 +191,32 @@ typedef struct {
 SSD_API size_t ssd_fused_state_workspace_bytes(const ssd_fused_state_params_t* prm);
 SSD_API int ssd_fused_state_fwd(const ssd_fused_state_params_t* prm, ssd_stream_t stream);
 
-/* Reads back (synchronously, after synchronising `stream`) the status word that the last
- * ssd_fused_state_fwd on this workspace left, and the library-held status of the tcgen05
- * chunk bmm / chunk scan kernels on the current device: SSD_OK, or SSD_ERR_TIMEOUT if a
- * bounded device wait gave up (outputs are then incomplete).  Optional: a healthy run never
- * sets it.  Has no counterpart in the reference, whose waits are unbounded
+/* Reads back (synchronously, after synchronising `stream`) every bounded-wait status word
+ * on the current device: the one the last ssd_fused_state_fwd on `workspace` left -- or,
+ * with workspace == NULL, the one the last ssd_fused_state_fwd_static left in the library's
+ * own scratch -- and the library-held words of ssd_chunk_state_fwd's tcgen05 route and of
+ * the tcgen05 chunk bmm / chunk scan kernels.  Returns SSD_OK, or SSD_ERR_TIMEOUT if a
+ * bounded device wait gave up (outputs are then incomplete; ssd_last_error() names the
+ * kernel and the wait).  The library-held words are cleared by the call that reports them;
+ * a caller's workspace header is the caller's to clear (SSD_FUSED_WORKSPACE_HEADER_BYTES),
+ * and the static scratch header is cleared by the next static call, so a static caller
+ * checks BEFORE its next static call.  Optional: a healthy run never sets a word.  Has no
+ * counterpart in the reference, whose waits are unbounded
  * (kernels/fused_concurrent.py:82-84,205-208). */
 SSD_API int ssd_check_status(void* workspace, ssd_stream_t stream);
+
+/* Test hooks.  No counterpart in the reference.
+ *   ssd_debug_set_wait_limit_cycles: SM clock cycles a device-side wait may last before it
+ *     gives up (process-wide, read at launch; <= 0 restores the default of 4e9, about two
+ *     seconds).  A wait that gives up never traps or spins on: the CTA records a wait code,
+ *     lets its copies in flight land, frees its tensor memory and returns.
+ *   ssd_debug_set_flags: SSD_DEBUG_DROP_CARRY_FLAGS makes the fused kernel skip publishing its
+ *     carry flags, so that a CTA which needs a carried state waits for a flag that nothing
+ *     sets, runs into the limit and the call ends with SSD_ERR_TIMEOUT from ssd_check_status.
+ *     This exists to test that path with a short limit; 0 restores normal operation. */
+#define SSD_DEBUG_DROP_CARRY_FLAGS 1
+SSD_API void ssd_debug_set_wait_limit_cycles(long long cycles);
+SSD_API void ssd_debug_set_flags(int flags);
 
 /* ------------------------------------------------------------------------------------
  * 4b. ssd_fused_state_fwd without a caller-supplied workspace.  It has no counterpart in

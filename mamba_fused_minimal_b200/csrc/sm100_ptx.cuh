@@ -72,11 +72,11 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// Every device-side wait in this library is bounded: after kWaitLimitCycles SM clocks
-// (about two seconds) without progress the waiter raises the CTA's abort flag, records
-// `code` in the global status word and returns false; every other waiter in the CTA sees
-// the flag and returns false too.  The limit is measured with the SM's own cycle counter,
-// which costs a few cycles to read, and only consulted once per 256 polls.
+// Every device-side wait in this library is bounded: after `limit` SM clocks (by default
+// kWaitLimitCycles, about two seconds) without progress the waiter raises the CTA's abort
+// flag, records `code` in the global status word and returns false; every other waiter in the
+// CTA sees the flag and returns false too.  The limit is measured with the SM's own cycle
+// counter, which costs a few cycles to read, and only consulted once per 256 polls.
 // The wait loops are inlined: a kernel that re-balances registers between its roles
 // (setmaxnreg) cannot contain real calls, ptxas refuses to allocate registers for it.
 #define SSD_SLOWPATH __forceinline__
@@ -85,6 +85,7 @@ constexpr long long kWaitLimitCycles = 4000000000ll;
 struct WaitCtx {
   volatile int* abort_flag;   // shared memory, one per CTA
   int* status;                // global memory, one per launch
+  long long limit;            // SM cycles a wait may last
 };
 
 // `sleep_ns` > 0 makes the waiter back off between polls: for roles that wait long and are
@@ -99,7 +100,7 @@ __device__ SSD_SLOWPATH bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitC
       if (*w.abort_flag) return false;
       const long long now = clock64();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitCycles) {
+      if (now - t0 > w.limit) {
         *w.abort_flag = 1;
         atomicCAS(w.status, 0, code);
         return false;
@@ -133,7 +134,7 @@ __device__ SSD_SLOWPATH bool flag_wait(const uint32_t* flag, uint32_t target, Wa
       if (*w.abort_flag) return false;
       const long long now = clock64();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitCycles) {
+      if (now - t0 > w.limit) {
         *w.abort_flag = 1;
         atomicCAS(w.status, 0, code);
         return false;

@@ -1,5 +1,6 @@
 // extern "C" entry points of libssd_b200.so: argument validation and dispatch.
 // Declarations and the reference functions each one replaces: include/ssd_b200.h.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -18,6 +19,12 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 const char* get_error() { return g_error; }
+
+// about two seconds of SM clocks
+static std::atomic<long long> g_wait_limit_cycles{4000000000ll};
+static std::atomic<int> g_debug_flags{0};
+long long wait_limit_cycles() { return g_wait_limit_cycles.load(std::memory_order_relaxed); }
+int debug_flags() { return g_debug_flags.load(std::memory_order_relaxed); }
 
 namespace {
 
@@ -192,14 +199,38 @@ int ssd_fused_state_fwd(const ssd_fused_state_params_t* prm, ssd_stream_t stream
   return launch_state_passing(sp, st);
 }
 
+void ssd_debug_set_wait_limit_cycles(long long cycles) {
+  g_wait_limit_cycles.store(cycles > 0 ? cycles : 4000000000ll, std::memory_order_relaxed);
+}
+void ssd_debug_set_flags(int flags) { g_debug_flags.store(flags, std::memory_order_relaxed); }
+
 int ssd_check_status(void* workspace, ssd_stream_t stream) {
-  SSD_REQUIRE(workspace != nullptr, SSD_ERR_BAD_ARGUMENT, "workspace is NULL");
   SSD_CUDA_OK(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
   int status = 0;
-  SSD_CUDA_OK(cudaMemcpy(&status, workspace, sizeof(int), cudaMemcpyDeviceToHost));
-  if (status != 0) {
-    set_error("a bounded device-side wait gave up (wait code %d); outputs are incomplete and the "
-              "workspace header must be cleared before reuse", status);
+  if (workspace != nullptr) {
+    SSD_CUDA_OK(cudaMemcpy(&status, workspace, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) {
+      set_error("a bounded device-side wait gave up (wait code %d); outputs are incomplete and the "
+                "workspace header (SSD_FUSED_WORKSPACE_HEADER_BYTES) must be cleared before reuse", status);
+      return SSD_ERR_TIMEOUT;
+    }
+  } else {
+    // no workspace: the caller used ssd_fused_state_fwd_static, whose header is in the library
+    const int rc = static_scratch_wait_status(&status);
+    if (rc != SSD_OK) return rc;
+    if (status != 0) {
+      set_error("a bounded device-side wait of the last ssd_fused_state_fwd_static call gave up (wait code %d); "
+                "its outputs are incomplete (the next static call clears the header)", status);
+      return SSD_ERR_TIMEOUT;
+    }
+  }
+  // ssd_chunk_state_fwd's tcgen05 route keeps its status word in the library too
+  int so_code = 0;
+  const int rc_so = states_only_wait_status(&so_code);
+  if (rc_so != SSD_OK) return rc_so;
+  if (so_code != 0) {
+    set_error("a bounded device-side wait of ssd_chunk_state_fwd gave up (wait code %d); the per-chunk states "
+              "are incomplete", so_code);
     return SSD_ERR_TIMEOUT;
   }
   // the chunk bmm / chunk scan kernels keep their wait status in the library (they use no workspace)

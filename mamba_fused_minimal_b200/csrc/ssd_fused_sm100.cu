@@ -148,6 +148,8 @@ struct FusedArgs {
   int mode;               // 0: state passing fused; 1: per-chunk states only
   int defer;              // non-zero: segments that start inside a strip start from zero; the
                           // carried state is added afterwards by segment_fixup_kernel
+  int debug;              // test hooks (ssd_debug_set_flags); 0 in normal use
+  long long wait_limit;   // SM cycles a device-side wait may last
 };
 
 
@@ -234,7 +236,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   // (an mbarrier instead of bar.sync so that the wait is bounded like the rest)
   auto bar_epi_sync = [&](int hd) { return bars + 8u * (C::B_EPI + hd); };
   volatile int* ctl = reinterpret_cast<volatile int*>(smem + C::OFF_CTL);   // [0] abort, [1] tmem, [2] epoch
-  WaitCtx wc{ctl, a.status};
+  WaitCtx wc{ctl, a.status, a.wait_limit};
 
   if (tid == 0) {
     for (int s = 0; s < C::NS; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), HPC); }
@@ -681,7 +683,10 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         ok = mbar_wait(bar_epi_sync(hd), epi_syncs & 1, wc, kWaitGroup);
         ++epi_syncs;
         if (!ok) break;
-        if ((tid & 127) == 0) st_release_gpu(a.flags + (size_t)blockIdx.x * HPC + hd, epoch_target);
+        // (test hook: with SSD_DEBUG_DROP_CARRY_FLAGS the flag is never published, so that the
+        // next CTA's bounded wait runs out)
+        if ((tid & 127) == 0 && !(a.debug & SSD_DEBUG_DROP_CARRY_FLAGS))
+          st_release_gpu(a.flags + (size_t)blockIdx.x * HPC + hd, epoch_target);
       }
     }
     bulk_wait_all();            // this thread's bulk copies are complete before the CTA retires
@@ -903,6 +908,8 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   a.states_dtype = p.states_dtype;
   a.clamp_decay = p.clamp_decay;
   a.mode = mode;
+  a.debug = debug_flags();
+  a.wait_limit = wait_limit_cycles();
 
   const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
   int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
@@ -993,6 +1000,17 @@ int make_cb_map(CUtensorMap* map, const void* base, int L, int ngroups, int nchu
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled (cb) failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
+
+int states_only_wait_status(int* code) {
+  int hdr[4] = {0, 0, 0, 0};
+  SSD_CUDA_OK(cudaMemcpyFromSymbol(hdr, g_states_only_header, sizeof(hdr)));
+  *code = hdr[0];
+  if (hdr[0] != 0) {
+    const int zero = 0;
+    SSD_CUDA_OK(cudaMemcpyToSymbol(g_states_only_header, &zero, sizeof(zero)));
+  }
   return SSD_OK;
 }
 

@@ -60,6 +60,7 @@ struct BmmArgs {
   int64_t out_s[5];                  // b, c, g, i, j (elements; j stride is 1)
   int out_dtype;
   int L, K, ngroups;
+  long long wait_limit;              // SM cycles a device-side wait may last
 };
 
 // Status word of the bmm kernel's bounded waits.
@@ -79,7 +80,7 @@ bmm_chunk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t off_ctl = off_b + kboxes * b_bytes;                          // 2 barriers, abort flag, tmem address
   const uint32_t bar_load = sbase + off_ctl, bar_acc = sbase + off_ctl + 8;
   volatile int* ctl = reinterpret_cast<volatile int*>(smem + off_ctl + 16);   // [0] abort, [1] tmem
-  WaitCtx wc{ctl, a.status};
+  WaitCtx wc{ctl, a.status, a.wait_limit};
 
   const int mt = blockIdx.x;
   const int c = blockIdx.y / a.ngroups, g = blockIdx.y % a.ngroups;
@@ -205,6 +206,7 @@ struct ScanArgs {
   int64_t D_stride;
   int D_dtype, D_has_hdim;
   int L, seqlen, nheads, ngroups, nchunks;
+  long long wait_limit;
 };
 
 __device__ int g_scan_status[4];
@@ -233,7 +235,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
   auto bar_free = [&](int i) { return bars + 40 + 8u * i; };
   auto bar_a_ready = [&](int i) { return bars + 64 + 8u * i; };
   volatile int* ctl = reinterpret_cast<volatile int*>(smem + kOffCtl + 80);     // [0] abort, [1] tmem
-  WaitCtx wc{ctl, a.status};
+  WaitCtx wc{ctl, a.status, a.wait_limit};
 
   const int mt = blockIdx.x;                       // 128-row tile inside the chunk
   const int h = blockIdx.y;
@@ -531,6 +533,7 @@ int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream) 
   a.L = L;
   a.K = p.k;
   a.ngroups = p.ngroups;
+  a.wait_limit = wait_limit_cycles();
   const int kboxes = p.k / 64;
   const int smem = kboxes * (kBmmRows * 128 + L * 128) + 64 + 1024;
   auto kern = p.in_dtype == SSD_BF16 ? bmm_chunk_kernel<__nv_bfloat16> : bmm_chunk_kernel<__half>;
@@ -609,6 +612,7 @@ int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream
   a.nheads = p.nheads;
   a.ngroups = p.ngroups;
   a.nchunks = nchunks;
+  a.wait_limit = wait_limit_cycles();
   const int smem = 2 * kScanRows * 128 + 2 * kScanP * 128 + kScanSlots * (kScanRows * kScanU * 4 + kScanU * 128) +
                    2 * 256 * 4 + 128 + 1024;
   auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_kernel<__nv_bfloat16> : chunk_scan_kernel<__half>;

@@ -8,6 +8,12 @@
 
 namespace ssd {
 
+// ---- settings shared by every launch (ssd_abi.cu) --------------------------------------
+// SM cycles a device-side wait may last before it gives up (ssd_debug_set_wait_limit_cycles).
+long long wait_limit_cycles();
+// Test hooks (ssd_debug_set_flags); 0 in normal use.
+int debug_flags();
+
 // ---- general kernels (ssd_general.cu) -------------------------------------------------
 int launch_chunk_cumsum(const ssd_chunk_cumsum_params_t& p, cudaStream_t stream);
 int launch_state_passing(const ssd_state_passing_params_t& p, cudaStream_t stream);
@@ -30,6 +36,12 @@ int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why);
 size_t fused_fast_workspace_bytes(const ssd_fused_state_params_t& p);
 // mode 0: chunk state + state passing; mode 1: per-chunk states only (p.states required).
 int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream);
+// Reads (and clears when set) the wait status word of launches in the states-only mode, which
+// have no workspace, on the current device; *code = 0 when no wait gave up.
+int states_only_wait_status(int* code);
+// The same for the header of the static scratch array (ssd_static_scratch.cu); the word is read,
+// not cleared: the next static call clears the whole header.
+int static_scratch_wait_status(int* code);
 
 // 4-D tensor map over a 16-bit (b, l, heads, inner) tensor whose innermost dimension is
 // contiguous (strides in elements: b, l, heads, inner); box = 64 inner elements x 1 head x

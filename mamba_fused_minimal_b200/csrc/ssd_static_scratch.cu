@@ -46,6 +46,15 @@ int static_scratch_address(void** out) {
 }
 
 }  // namespace
+
+int static_scratch_wait_status(int* code) {
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != SSD_OK) return rc;
+  SSD_CUDA_OK(cudaMemcpy(code, scratch, sizeof(int), cudaMemcpyDeviceToHost));
+  return SSD_OK;
+}
+
 }  // namespace ssd
 
 using namespace ssd;

@@ -3,6 +3,7 @@
 // device), looks up the current CUDA stream and calls the C ABI (include/ssd_b200.h).
 // Shape assertions live in the Python shims so that they raise AssertionError like the
 // reference; this layer raises RuntimeError for anything the C ABI rejects.
+#include <c10/cuda/CUDAFunctions.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
@@ -11,6 +12,8 @@
 #include <map>
 #include <mutex>
 #include <optional>
+#include <utility>
+#include <vector>
 
 #include "ssd_b200.h"
 
@@ -93,20 +96,22 @@ void fill_state_inputs(ssd_state_inputs_t& in, const Tensor& B, const Tensor& x,
   }
 }
 
-// One zero-initialised workspace per device, grown on demand.  The fused kernel leaves its
-// header consistent after every call, so the buffer is reused without clearing; work on
-// one device is assumed to be issued from one stream at a time, as the reference does.
+// One zero-initialised workspace per (device, stream), grown on demand.  The fused kernel
+// leaves its header consistent after every call, so a buffer is reused without clearing.
+// Calls on different streams of one device get different buffers (their kernels may overlap
+// and would otherwise share flags and carry slots); calls on one stream are ordered.
 struct Workspace {
   Tensor buf;
 };
 std::mutex g_ws_mutex;
-std::map<int, Workspace> g_ws;
+std::map<std::pair<int, void*>, Workspace> g_ws;
 
-Tensor get_workspace(const Tensor& like, size_t bytes) {
+Tensor get_workspace(const Tensor& like, size_t bytes, ssd_stream_t stream) {
   std::lock_guard<std::mutex> lock(g_ws_mutex);
-  Workspace& w = g_ws[like.device().index()];
+  Workspace& w = g_ws[{(int)like.device().index(), (void*)stream}];
   if (!w.buf.defined() || (size_t)w.buf.numel() < bytes) {
     w.buf = torch::zeros({(int64_t)bytes}, torch::dtype(torch::kUInt8).device(like.device()));
+    // the fill runs on the current stream, which is the stream the buffer serves
   }
   return w.buf;
 }
@@ -274,10 +279,11 @@ std::tuple<Tensor, Tensor> fused_state_fwd(const Tensor& B, const Tensor& x, con
   p.clamp_decay = clamp_decay ? 1 : 0;
   p.force_general = force_general ? 1 : 0;
   const size_t need = ssd_fused_state_workspace_bytes(&p);
-  Tensor ws = get_workspace(x, need);
+  const ssd_stream_t stream = current_stream(x);
+  Tensor ws = get_workspace(x, need, stream);
   p.workspace = ws.data_ptr();
   p.workspace_bytes = ws.numel();
-  check_rc(ssd_fused_state_fwd(&p, current_stream(x)), "ssd_fused_state_fwd");
+  check_rc(ssd_fused_state_fwd(&p, stream), "ssd_fused_state_fwd");
   return {out, fin};
 }
 
@@ -293,19 +299,36 @@ void fused_state_fwd_static(const Tensor& B, const Tensor& x, const Tensor& dt, 
   fill_state_inputs(p.in, B, x, dt, dA_cumsum, std::nullopt, hold);
   check_cuda(out, x, "out");
   check_cuda(fin, x, "final_states");
-  TORCH_CHECK(out.dim() == 5 && out.stride(4) == 1, "out must be (b, c, h, p, n) with a contiguous last dimension");
-  TORCH_CHECK(fin.dim() == 4 && fin.stride(3) == 1 && fin.scalar_type() == at::kFloat,
+  // every caller-provided tensor is written (or read) by the kernels at these exact sizes
+  const int64_t batch = x.size(0), nheads = x.size(2), headdim = x.size(3), dstate = B.size(3);
+  const int64_t nchunks = dt.size(2);
+  TORCH_CHECK(B.size(0) == batch && B.size(1) == x.size(1) && nheads % B.size(2) == 0, "B must be (b, l, g, n) with g dividing h");
+  TORCH_CHECK(dt.size(0) == batch && dt.size(1) == nheads && nchunks == (x.size(1) + dt.size(3) - 1) / dt.size(3) &&
+                  dA_cumsum.sizes() == dt.sizes(),
+              "dt and dA_cumsum must be (b, h, ceil(l / L), L)");
+  TORCH_CHECK(out.dim() == 5 && out.stride(4) == 1 && out.size(0) == batch && out.size(1) == nchunks &&
+                  out.size(2) == nheads && out.size(3) == headdim && out.size(4) == dstate,
+              "out must be (b, c, h, p, n) = (", batch, ", ", nchunks, ", ", nheads, ", ", headdim, ", ", dstate,
+              ") with a contiguous last dimension");
+  TORCH_CHECK(fin.dim() == 4 && fin.stride(3) == 1 && fin.scalar_type() == at::kFloat && fin.size(0) == batch &&
+                  fin.size(1) == nheads && fin.size(2) == headdim && fin.size(3) == dstate,
               "final_states must be fp32 (b, h, p, n) with a contiguous last dimension");
   if (initial_states.has_value()) {
     check_cuda(*initial_states, x, "initial_states");
-    TORCH_CHECK(initial_states->stride(3) == 1, "initial_states must be contiguous in its last dimension");
+    TORCH_CHECK(initial_states->dim() == 4 && initial_states->stride(3) == 1 && initial_states->size(0) == batch &&
+                    initial_states->size(1) == nheads && initial_states->size(2) == headdim &&
+                    initial_states->size(3) == dstate,
+                "initial_states must be (b, h, p, n) with a contiguous last dimension");
     p.initial_states = initial_states->data_ptr();
     p.init_dtype = dtype_code(*initial_states, "initial_states");
     copy_strides(p.init_stride, *initial_states, {0, 1, 2});
   }
   if (states_in.has_value()) {
     check_cuda(*states_in, x, "states");
-    TORCH_CHECK(states_in->stride(4) == 1, "states must be contiguous in its last dimension");
+    TORCH_CHECK(states_in->dim() == 5 && states_in->stride(4) == 1 && states_in->size(0) == batch &&
+                    states_in->size(1) == nchunks && states_in->size(2) == nheads && states_in->size(3) == headdim &&
+                    states_in->size(4) == dstate,
+                "states must be (b, c, h, p, n) with a contiguous last dimension");
     p.states = states_in->data_ptr();
     p.states_dtype = dtype_code(*states_in, "states");
     copy_strides(p.states_stride, *states_in, {0, 1, 2, 3});
@@ -337,6 +360,10 @@ void seqpar_fixup(const Tensor& Z_all, const Tensor& logP_all, int64_t rank, con
   TORCH_CHECK(out.dim() == 5 && out.stride(4) == 1 && out.stride(3) == out.size(4), "out must be (b, c, h, p, n) with dense (p, n)");
   TORCH_CHECK(final_states.dim() == 4 && final_states.stride(3) == 1 && final_states.stride(2) == final_states.size(3),
               "final_states must be (b, h, p, n) with dense (p, n)");
+  TORCH_CHECK(final_states.size(0) == out.size(0) && final_states.size(1) == out.size(2) &&
+                  final_states.size(2) == out.size(3) && final_states.size(3) == out.size(4),
+              "final_states must be (b, h, p, n) of the same b, h, p, n as out (b, c, h, p, n)");
+  TORCH_CHECK(rank >= 0 && rank < Z_all.size(0), "rank ", rank, " outside world ", Z_all.size(0));
   c10::cuda::CUDAGuard guard(out.device());
   ssd_seqpar_fixup_params_t p{};
   p.Z_all = Z_all.data_ptr<float>();
@@ -363,19 +390,26 @@ void seqpar_fixup(const Tensor& Z_all, const Tensor& logP_all, int64_t rank, con
   check_rc(ssd_seqpar_fixup(&p, current_stream(out)), "ssd_seqpar_fixup");
 }
 
-// Synchronises and reports whether the last fused call on this device hit a wait limit.
+// Synchronises the current stream and reports whether a device-side wait of any call made so
+// far on this device gave up: the cached workspaces of the fused entry point (a workspace whose
+// status word is set is cleared for reuse before the error is raised), the static scratch of
+// fused_state_fwd_static, and the status words the library keeps for its other tcgen05 kernels.
 void check_status(const Tensor& like) {
   c10::cuda::CUDAGuard guard(like.device());
-  Tensor ws;
+  std::vector<Tensor> bufs;
   {
     std::lock_guard<std::mutex> lock(g_ws_mutex);
-    auto it = g_ws.find(like.device().index());
-    if (it == g_ws.end() || !it->second.buf.defined()) return;
-    ws = it->second.buf;
+    for (auto& kv : g_ws)
+      if (kv.first.first == (int)like.device().index() && kv.second.buf.defined()) bufs.push_back(kv.second.buf);
   }
-  const int rc = ssd_check_status(ws.data_ptr(), current_stream(like));
-  if (rc == SSD_ERR_TIMEOUT) ws.zero_();
-  check_rc(rc, "ssd_check_status");
+  const ssd_stream_t stream = current_stream(like);
+  if (bufs.size() > 1) c10::cuda::device_synchronize();     // other streams' calls as well
+  for (Tensor& ws : bufs) {
+    const int rc = ssd_check_status(ws.data_ptr(), stream);
+    if (rc == SSD_ERR_TIMEOUT) ws.zero_();
+    check_rc(rc, "ssd_check_status");
+  }
+  check_rc(ssd_check_status(nullptr, stream), "ssd_check_status (static scratch)");
 }
 
 Tensor bmm_chunk_fwd(const Tensor& a, const Tensor& b, int64_t chunk_size, const OptTensor& seq_idx, bool causal,
@@ -507,6 +541,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("seqpar_fixup", &seqpar_fixup, py::arg("Z_all"), py::arg("logP_all"), py::arg("rank"),
         py::arg("dA_chunk_last"), py::arg("out"), py::arg("final_states"));
   m.def("check_status", &check_status, py::arg("like"));
+  m.def("debug_set_wait_limit_cycles", [](int64_t cycles) { ssd_debug_set_wait_limit_cycles((long long)cycles); });
+  m.def("debug_set_flags", [](int64_t flags) { ssd_debug_set_flags((int)flags); });
   m.def("bmm_chunk_fwd", &bmm_chunk_fwd, py::arg("a"), py::arg("b"), py::arg("chunk_size"),
         py::arg("seq_idx") = py::none(), py::arg("causal") = false, py::arg("output_dtype") = py::none());
   m.def("chunk_scan_fwd", &chunk_scan_fwd, py::arg("cb"), py::arg("x"), py::arg("dt"), py::arg("dA_cumsum"),

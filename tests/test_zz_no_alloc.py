@@ -35,6 +35,9 @@ def _run_pair(cuda_device, shape, dtype, init, force_general, seeds=(31, 32)):
         C.fused_state_fwd_static(inp["B"], inp["x"], dt, dA, out, fin, initial_states=init_d,
                                  force_general=force_general)
         torch.cuda.synchronize()
+        # no bounded wait gave up, neither on the cached workspace nor on the static scratch
+        # (its status word is read before the next static call clears the header)
+        C.check_status(inp["x"])
         assert torch.equal(out, ref_out), f"seed {seed}: out differs"
         assert torch.equal(fin, ref_fin), f"seed {seed}: final_states differs"
 
