@@ -69,7 +69,7 @@ def _close16(a, b, what):
 CASES = [
     # b, l, h, g, L, (|A| range), initial states, caller's states buffer
     dict(id="one_strip_slow", b=1, l=262144, h=2, g=1, L=64, a=(0.01, 0.05), init=False, states_buf=False),
-    dict(id="one_strip_bench_decay", b=1, l=131072, h=2, g=1, L=64, a=(1.0, 16.0), init=True, states_buf=False),
+    dict(id="one_strip_bench_decay", b=1, l=196608, h=2, g=1, L=64, a=(1.0, 16.0), init=True, states_buf=False),
     dict(id="hpc1_groups_ragged", b=1, l=64 * 512 + 37, h=6, g=2, L=64, a=(0.02, 0.2), init=True, states_buf=False),
     dict(id="two_batches_L256", b=2, l=256 * 1200 + 100, h=2, g=1, L=256, a=(0.002, 0.01), init=False, states_buf=True),
 ]
@@ -103,12 +103,14 @@ def test_deferred_carry_against_oracle_and_plain_route(cuda_device, case):
     assert rel_err(fin32.cpu(), ref_fin) <= 1e-3
     assert rel_err(out32.cpu(), ref_out) <= 1e-3
     _close16(out, ref_out.to(torch.bfloat16), "passed states (bf16)")
-    # first and last 64 chunks element by element against the bf16-rounded oracle: at most one
-    # bf16 step apart (the second pass rounds a touched element a second time)
+    # first and last 64 chunks element by element.  The second pass reads the 16-bit zero-carry
+    # value, adds the carried term in fp32 and rounds again: one rounding of the result (relative
+    # to the element) plus one of the zero-carry value (relative to ITS size, which is bounded
+    # by the tensor's scale, not by the element: the two terms may cancel).
     for sl in (slice(0, 64), slice(nchunks - 64, nchunks)):
         a = out[:, sl].float().cpu()
         r = ref_out[:, sl]
-        assert ((a - r).abs() <= 2.0 ** -7 * r.abs() + 1e-3 * r.abs().max()).all()
+        assert ((a - r).abs() <= 2.0 ** -7 * r.abs() + 2.0 ** -8 * ref_out.abs().max()).all()
     if buf is not None:
         ref_states = O.chunk_state_fwd(inp["B"], inp["x"], dt.cpu(), dA.cpu(), exp_impl="ex2")
         assert rel_err(buf.cpu(), ref_states) <= 1e-3
