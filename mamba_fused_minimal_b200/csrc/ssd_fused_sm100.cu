@@ -299,11 +299,11 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
               const uint32_t st = sbase + C::OFF_STAGES + s * C::STAGE_BYTES;
               const int l0 = c * L + ks * kKT;
               mbar_expect_tx(bar_full(s), C::LOAD_BYTES);
-              tma_load_4d_hint(st, &tmap_B, bar_full(s), 0, g, l0, b, keep);
-              tma_load_4d_hint(st + C::RAWB_BYTES / 2, &tmap_B, bar_full(s), 64, g, l0, b, keep);
-#pragma unroll
-              for (int hd = 0; hd < HPC; ++hd)
-                tma_load_4d_hint(st + C::OFF_XT + hd * C::X_BYTES, &tmap_x, bar_full(s), 0, h0 + hd, l0, b, stream_once);
+              // one copy for the raw B tile (both 64-column halves, one after the other) and one for
+              // the x tiles of all the CTA's heads: few large copies keep the copy engine busier than
+              // many small ones
+              tma_load_5d_hint(st, &tmap_B, bar_full(s), 0, l0, 0, g, b, keep);
+              tma_load_4d_hint(st + C::OFF_XT, &tmap_x, bar_full(s), 0, l0, h0, b, stream_once);
             }
           }
         }
@@ -812,9 +812,40 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-int make_map(CUtensorMap* map, const void* base, int dtype, int inner, int heads, int seqlen, int batch,
-             const int64_t* stride /* b, l, h, inner */) {
-  return make_rows_map(map, base, dtype, inner, heads, seqlen, batch, stride, kKT);
+// x (b, l, h, p) as a 4-D map with the dimensions ordered (p, l, h, b): a box of 64 x kKT x heads x 1
+// lands in shared memory as one (kKT x 64) tile per head, one after the other, each in the
+// 128-byte-swizzled arrangement the MMA reads.
+int make_x_map(CUtensorMap* map, const void* base, int dtype, int nheads, int seqlen, int batch, const int64_t* stride,
+               int heads_per_box) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)kP, (cuuint64_t)seqlen, (cuuint64_t)nheads, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)stride[1] * 2, (cuuint64_t)stride[2] * 2, (cuuint64_t)stride[0] * 2};
+  const cuuint32_t box[4] = {64, (cuuint32_t)kKT, (cuuint32_t)heads_per_box, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled (x) failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
+
+// B (b, l, g, n = 128) as a 5-D map (n low 64, l, n high 2, g, b): a box of 64 x kKT x 2 lands as
+// two (kKT x 64) tiles, columns 0-63 then 64-127.
+int make_B_map(CUtensorMap* map, const void* base, int dtype, int ngroups, int seqlen, int batch, const int64_t* stride) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[5] = {64, (cuuint64_t)seqlen, 2, (cuuint64_t)ngroups, (cuuint64_t)batch};
+  const cuuint64_t strides[4] = {(cuuint64_t)stride[1] * 2, 128, (cuuint64_t)stride[2] * 2, (cuuint64_t)stride[0] * 2};
+  const cuuint32_t box[5] = {64, (cuuint32_t)kKT, 2, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 5, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled (B) failed with CUresult %d", (int)r);
+  return SSD_OK;
 }
 
 // 5-D map over the 16-bit passed states (b, c, h, p, n) with (p, n) dense; box = 32 columns (one
@@ -854,9 +885,9 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   using C = Cfg<HPC>;
   const ssd_state_inputs_t& in = p.in;
   CUtensorMap mx, mB;
-  int rc = make_map(&mx, in.x, in.in_dtype, kP, in.nheads, in.seqlen, in.batch, in.x_stride);
+  int rc = make_x_map(&mx, in.x, in.in_dtype, in.nheads, in.seqlen, in.batch, in.x_stride, HPC);
   if (rc != SSD_OK) return rc;
-  rc = make_map(&mB, in.B, in.in_dtype, kN, in.ngroups, in.seqlen, in.batch, in.B_stride);
+  rc = make_B_map(&mB, in.B, in.in_dtype, in.ngroups, in.seqlen, in.batch, in.B_stride);
   if (rc != SSD_OK) return rc;
   CUtensorMap mo = mx;                  // a valid map even where the kernel never touches it
   if (mode == 0 && p.out_dtype != SSD_F32) {
