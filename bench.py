@@ -22,6 +22,15 @@ Prints ONE JSON line (rank 0):
             against the measured HBM copy bandwidth of this pool (MEASURED_PEAKS.json)
   cpu_baseline  the same chunked math in torch on the host cores, on a bounded sample
 
+Extras on the same line (key "extra", measured after the headline, outside its timed region):
+  seq1m        ONE 1 048 576-token sequence sharded along the sequence over the N ranks (strong
+               scaling; chunk cumsum + local scan + one NCCL all-gather of slice summaries +
+               cross-rank fix-up), with the same step on the whole sequence on one GPU measured in
+               the same run, the speed-up, the per-phase split and the clocks
+  cfg2_strong  the headline shape with its 80 heads split over the N ranks (80 / N heads each)
+  seqpar_check a 32 768-token sequence through the sequence-parallel path over the real process
+               group, every rank's slice compared with a single-GPU run of the whole sequence
+
 `--impl reference` times that CPU implementation (the oracle's restatement of the
 reference's algorithm; the reference itself is Triton and has no CPU build) on all host
 threads and prints the same line shape with "impl": "reference".
@@ -179,28 +188,41 @@ def run_reference_arm(args, rank, world):
 SEQ1M = dict(name="seq-1m", batch=1, seqlen=1048576, nheads=80, headdim=64, ngroups=1, dstate=128, chunk_size=256)
 
 
-def run_seq1m(args, rank, world, local):
-    """Long-context case: ONE 1 M-token sequence, sharded along the sequence over the ranks
-    (strong scaling).  A step = chunk cumsum of the slice + the sequence-parallel fused state
-    path (local scan from a zero carry, NCCL all-gather of slice summaries, fix-up)."""
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+def _sync_barrier(dist):
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def _timed_steps(step, K, warmup, dist, dev):
+    """K steps bracketed by barrier + synchronize, CUDA events, max over ranks -> ms per step."""
+    for _ in range(warmup):
+        step()
+    _sync_barrier(dist)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        step()
+    e1.record()
+    _sync_barrier(dist)
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()) / K
+
+
+def seq_sharded_case(w, K, warmup, rank, world, dist, dev, sampler_index=None):
+    """One long sequence sharded along the sequence over the ranks.  Returns a dict (rank 0: filled)."""
     from mamba_fused_minimal_b200 import parallel as P
-    from mamba_fused_minimal_b200.kernels.fused_concurrent import _fused_chunk_state_state_passing_fwd_concurrent as fused
+    from mamba_fused_minimal_b200._ext import C as _C
+    from mamba_fused_minimal_b200.kernels._fused import _fused_chunk_state_state_passing_fwd as fused
     from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
     from mamba_fused_minimal_b200.kernels.ssd_chunk_state import _chunk_cumsum_fwd as cumsum
-    w = dict(SEQ1M)
-    if args.seqlen is not None:
-        w["seqlen"] = args.seqlen
-        w["name"] = f"seq-{args.seqlen}"
     L = w["chunk_size"]
     s0, s1 = P.shard_sequence(w["seqlen"], L, world, rank)
     d = generate_benchmark_data(1, s1 - s0, w["nheads"], w["headdim"], w["ngroups"], w["dstate"],
-                                dtype=torch.bfloat16, device=dev, seed=rank)
+                                dtype=torch.bfloat16, device=dev, seed=100 + rank)
     x, B, dt, A, bias = d["x"], d["B"], d["dt"], d["A"], d["dt_bias"]
 
     def step():
@@ -209,51 +231,176 @@ def run_seq1m(args, rank, world, local):
             return fused(B, x, dto, dA, torch.bfloat16)
         return P.seqpar_fused_state_fwd(B, x, dto, dA, torch.bfloat16)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
+    sampler = ClockSampler(sampler_index) if sampler_index is not None else None
     if sampler is not None:
         sampler.start()
-    K = args.steps
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for _ in range(K):
-        step()
-    end.record()
-    barrier()
-    total_ms = start.elapsed_time(end)
+    ms = _timed_steps(step, K, warmup, dist, dev)
     clocks = sampler.stop() if sampler is not None else None
-    from mamba_fused_minimal_b200._ext import C as _C
-    _C.check_status(x)
-    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+
+    # per-phase split on a few extra steps (events between the phases; not part of `ms`)
+    phases = None
     if dist is not None:
+        names = ["cumsum", "fused_and_segment_fixup", "logP_sum", "all_gather", "cross_rank_fixup"]
+        Kp = 5
+        acc = [0.0] * len(names)
+        for _ in range(Kp):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+            ev[0].record()
+            dA, dto = cumsum(dt, A, L, dt_bias=bias, dt_softplus=True)
+            ev[1].record()
+            buf, Z, logP = P.summary_buffer(1, w["nheads"], w["headdim"], w["dstate"], dev)
+            out, _ = fused(B, x, dto, dA, torch.bfloat16, final_states=Z)
+            ev[2].record()
+            dA_last = dA[:, :, :, -1]
+            torch.sum(dA_last, dim=-1, out=logP)
+            ev[3].record()
+            Z_all, logP_all = P.exchange_summaries(buf, (1, w["nheads"], w["headdim"], w["dstate"]))
+            ev[4].record()
+            if rank > 0:
+                _C.seqpar_fixup(Z_all, logP_all, rank, dA_last, out, Z)
+            ev[5].record()
+            _sync_barrier(dist)
+            for i in range(len(names)):
+                acc[i] += ev[i].elapsed_time(ev[i + 1]) / Kp
+        t = torch.tensor(acc, device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        phases = {n: round(v, 4) for n, v in zip(names, t.tolist())}
+        phases["note"] = "ms, max over ranks per phase, events between the phases (5 extra steps)"
+    _C.check_status(x)
+    del d, x, B, dt
+    torch.cuda.empty_cache()
+    peak, peak_kind = measured_peak()
+    path_bytes = algorithmic_bytes(w, with_cumsum=True)
+    gbs = path_bytes / (ms * 1e-3) / 1e9
+    return {"workload": w["name"], "seqlen": w["seqlen"], "nheads": w["nheads"], "world": world, "scaling": "strong",
+            "ms_per_step": ms, "tokens_per_s": w["seqlen"] / (ms * 1e-3), "steps": K,
+            "path_bytes_per_step": path_bytes, "achieved_gbs": gbs, "frac_of_world_x_peak": gbs / (peak * world),
+            "peak_kind": peak_kind, "phases": phases, "clocks": clocks}
+
+
+def head_sharded_case(w, K, warmup, rank, world, dist, dev, sampler_index=None):
+    """The headline shape with its heads split over the ranks (strong scaling, no collective on the
+    data path: every kernel is independent per head given the group's B)."""
+    from mamba_fused_minimal_b200 import parallel as P
+    from mamba_fused_minimal_b200.kernels.fused_concurrent import _fused_chunk_state_state_passing_fwd_concurrent as fused
+    from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_state import _chunk_cumsum_fwd as cumsum
+    (h0, h1), (g0, g1) = P.shard_heads(w["nheads"], w["ngroups"], world, rank)
+    L = w["chunk_size"]
+    d = generate_benchmark_data(w["batch"], w["seqlen"], h1 - h0, w["headdim"], g1 - g0, w["dstate"],
+                                dtype=torch.bfloat16, device=dev, seed=200 + rank)
+    x, B, dt, A, bias = d["x"], d["B"], d["dt"], d["A"], d["dt_bias"]
+
+    def step():
+        dA, dto = cumsum(dt, A, L, dt_bias=bias, dt_softplus=True)
+        return fused(B, x, dto, dA, torch.bfloat16)
+
+    sampler = ClockSampler(sampler_index) if sampler_index is not None else None
+    if sampler is not None:
+        sampler.start()
+    ms = _timed_steps(step, K, warmup, dist, dev)
+    clocks = sampler.stop() if sampler is not None else None
+    peak, peak_kind = measured_peak()
+    # every rank reads the whole B of its group(s): count it once per rank that holds it
+    wr = dict(w, nheads=h1 - h0, ngroups=g1 - g0)
+    per_rank = algorithmic_bytes(wr, with_cumsum=True)
+    gbs = per_rank * world / (ms * 1e-3) / 1e9
+    return {"workload": w["name"], "world": world, "scaling": "strong", "heads_per_rank": h1 - h0,
+            "ms_per_step": ms, "tokens_per_s": w["batch"] * w["seqlen"] / (ms * 1e-3), "steps": K,
+            "achieved_gbs": gbs, "frac_of_world_x_peak": gbs / (peak * world), "peak_kind": peak_kind,
+            "clocks": clocks}
+
+
+def seqpar_check(rank, world, dist, dev):
+    """The sequence-parallel path over the real process group against a single-GPU run of the whole
+    sequence on every rank (same seeded inputs everywhere).  Errors as max|a-b| / max|b|."""
+    from mamba_fused_minimal_b200 import parallel as P
+    from mamba_fused_minimal_b200.kernels.fused_concurrent import _fused_chunk_state_state_passing_fwd_concurrent as fused
+    from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_state import _chunk_cumsum_fwd as cumsum
+    b, l, h, L = 1, 32768, 8, 256
+    d = generate_benchmark_data(b, l, h, 64, 1, 128, dtype=torch.bfloat16, device=dev, seed=77)
+    # decays slow enough for a carried state to reach well into the next rank's slice
+    A = d["A"] * 0.002
+    dA_f, dt_f = cumsum(d["dt"], A, L, dt_bias=d["dt_bias"], dt_softplus=True)
+    out_f, fin_f = fused(d["B"], d["x"], dt_f, dA_f, torch.bfloat16)
+    s0, s1 = P.shard_sequence(l, L, world, rank)
+    dA, dt = cumsum(d["dt"][:, s0:s1], A, L, dt_bias=d["dt_bias"], dt_softplus=True)
+    out, fin = P.seqpar_fused_state_fwd(d["B"][:, s0:s1], d["x"][:, s0:s1], dt, dA, torch.bfloat16)
+    torch.cuda.synchronize()
+    c0 = s0 // L
+    scale = out_f.float().abs().max()
+    err_out = ((out.float() - out_f[:, c0:c0 + out.shape[1]].float()).abs().max() / scale).item()
+    # the state leaving this slice: the next slice's first passed state, or the final state
+    if c0 + out.shape[1] < out_f.shape[1]:
+        nxt, tol_kind = out_f[:, c0 + out.shape[1]].float(), 0.0
+    else:
+        nxt, tol_kind = fin_f, 1.0
+    err_fin = ((fin - nxt).abs().max() / nxt.abs().max()).item()
+    t = torch.tensor([err_out, err_fin if tol_kind == 1.0 else 0.0, err_fin if tol_kind == 0.0 else 0.0],
+                     device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    eo, ef, eb = t.tolist()
+    return {"world": world, "seqlen": l, "nheads": h, "max_err_out": eo, "max_err_final": ef,
+            "max_err_slice_boundary_state_vs_bf16_neighbour": eb,
+            "ok": bool(eo <= 1e-2 and ef <= 1e-3 and eb <= 1e-2),
+            "tolerance": "passed states 1e-2 of the tensor's max, final state 1e-3"}
+
+
+def run_extras(args, rank, world, local, dist, dev):
+    """The multi-GPU cases beyond the weak headline; returns the dict for the "extra" key."""
+    extra = {}
+    K = max(3, min(args.steps, 20))
+    idx = physical_gpu_index(local) if rank == 0 else None
+    seq = seq_sharded_case(dict(SEQ1M), K, 3, rank, world, dist, dev, sampler_index=idx)
+    if world > 1:
+        # the same step on the whole sequence on ONE GPU, measured in this run (every rank does it on
+        # its own GPU, nothing is exchanged; the maximum over ranks is kept)
+        one = seq_sharded_case(dict(SEQ1M), max(3, K // 2), 3, 0, 1, None, dev, sampler_index=idx)
+        t = torch.tensor([one["ms_per_step"]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        seq["world1_ms_per_step"] = float(t.item())
+        seq["world1_clocks"] = one["clocks"]
+        seq["speedup_over_world1"] = seq["world1_ms_per_step"] / seq["ms_per_step"]
+    extra["seq1m"] = seq
+    # (a step is ~0.1 ms: more of them, after a longer warm-up, so that the clocks have settled after
+    # the seconds of full load just before)
+    strong = head_sharded_case(dict(WORKLOAD), 5 * K, 20, rank, world, dist, dev, sampler_index=idx)
+    extra["cfg2_strong"] = strong
+    if world > 1:
+        extra["seqpar_check"] = seqpar_check(rank, world, dist, dev)
+    return extra
+
+
+def run_seq1m(args, rank, world, local):
+    """`--workload seq1m`: the long-context case as the line's own workload."""
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    w = dict(SEQ1M)
+    if args.seqlen is not None:
+        w["seqlen"] = args.seqlen
+        w["name"] = f"seq-{args.seqlen}"
+    r = seq_sharded_case(w, args.steps, args.warmup, rank, world, dist, dev,
+                         sampler_index=physical_gpu_index(local) if rank == 0 else None)
     if rank == 0:
-        ms = float(t.item()) / K
         peak, peak_kind = measured_peak()
-        path_bytes = algorithmic_bytes(w, with_cumsum=True)
-        gbs = path_bytes / (ms * 1e-3) / 1e9
         print(json.dumps({
-            "metric": "ssd_state_path_tokens_per_s", "value": w["seqlen"] / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": K, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "metric": "ssd_state_path_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": dict(workload=w["name"], **{k: v for k, v in w.items() if k != "name"},
                            parallelism=f"sequence sharded over {world} GPU(s); all-gather of slice summaries + fix-up",
-                           l2="inputs exceed the 126 MB L2; no explicit flush", path_bytes_per_step=path_bytes),
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak * world, "unit": "GB/s",
-                         "frac": gbs / (peak * world), "traffic": None, "peak_kind": peak_kind,
+                           l2="inputs exceed the 126 MB L2; no explicit flush", path_bytes_per_step=r["path_bytes_per_step"]),
+            "roofline": {"bound": "hbm", "achieved": r["achieved_gbs"], "peak": peak * world, "unit": "GB/s",
+                         "frac": r["frac_of_world_x_peak"], "traffic": None, "peak_kind": peak_kind,
                          "kernel": "whole step (cumsum + fused + exchange + fix-up), all GPUs"},
-            "e2e": None,
-            # per rank: cumsum, fused kernel, segment fix-up, and (ranks > 0) the cross-rank fix-up
-            "gpu_launches": (3 if world == 1 else 4) * K, "clocks": clocks}), flush=True)
+            "phases": r["phases"], "e2e": None,
+            # per rank: cumsum, fused kernel, segment fix-up, logP sum, and (ranks > 0) the cross-rank fix-up
+            "gpu_launches": (3 if world == 1 else 5) * args.steps, "clocks": r["clocks"]}), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -271,6 +418,7 @@ def main():
     ap.add_argument("--workload", default="mamba2-2.7b-layer", choices=["mamba2-2.7b-layer", "seq1m"],
                     help="seq1m: the 1 M-token sequence-parallel case (extra; the default is the contract's workload)")
     ap.add_argument("--seqlen", type=int, default=None, help="seq1m only: override the sequence length")
+    ap.add_argument("--no-extras", action="store_true", help="skip the extra multi-GPU cases (key \"extra\")")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -280,6 +428,10 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
+    if world > 1:
+        # the only collectives are a 21 MB all-gather and a few scalars: no in-switch reduction needed,
+        # and a rank that dies while bound to a multicast object would disturb its peers
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
@@ -417,6 +569,11 @@ def main():
         barrier()
         e2e_ms = e0.elapsed_time(e1) / Ke
     clocks = sampler.stop() if sampler is not None else None
+    del out, fin, dA, dto
+    torch.cuda.empty_cache()
+    extra = None
+    if not args.no_extras and args.batch is None:
+        extra = run_extras(args, rank, world, local, dist, dev)
 
     # ---- max over ranks ---------------------------------------------------------------
     stats = torch.tensor([total_ms, e2e_ms, statistics.mean(fused_ms)], device=dev, dtype=torch.float64)
@@ -455,6 +612,8 @@ def main():
             "gpu_launches": 2 * K,
             "clocks": clocks,
         }
+        if extra is not None:
+            line["extra"] = extra
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
             tok_s, t, n = cpu_hot_path(WORKLOAD["batch"], threads, 20)

@@ -278,9 +278,11 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     if (warp == C::EPI_WARPS) {
       // ============================== TMA producer ====================================
       if (lane == 0) {
-        // B is read once per head of its group and should stay in L2 between those reads;
-        // x is read exactly once.
-        const uint64_t keep = l2_policy_evict_last(), stream_once = l2_policy_evict_first();
+        // x is read exactly once: its lines are the first to go.  B is re-read once per head pair of
+        // its group and stays in L2 by being re-used; it is NOT marked evict-last: such lines outlive
+        // the launch and a long sequence's worth of them (268 MB at a million tokens) would occupy the
+        // L2 for whatever runs next (measured: the next launches ran 20 % slower).
+        const uint64_t keep = l2_policy_evict_normal(), stream_once = l2_policy_evict_first();
         uint32_t it = 0;
         bool ok = true;
         for (int j = 0; j < rg.m && ok; ++j) {
