@@ -219,6 +219,33 @@ SSD_API void ssd_debug_set_wait_limit_cycles(long long cycles);
 SSD_API void ssd_debug_set_flags(int flags);
 
 /* ------------------------------------------------------------------------------------
+ * 4a. the whole state path in one call: chunk cumsum (1) + fused chunk state and state
+ *    passing (4).  Replaces the pair of calls the reference's pipelines make,
+ *    _chunk_cumsum_fwd then _fused_chunk_state_state_passing_fwd_concurrent
+ *    (main.py:96-100; kernels/ssd_chunk_state.py:176-199, kernels/fused_concurrent.py:255-331).
+ *
+ *    `cumsum` describes the raw dt, A, dt_bias and the two fp32 outputs dt_out and dA_cumsum
+ *    ((b, h, c, L) contiguous) exactly as for ssd_chunk_cumsum_fwd; `fused` describes x, B,
+ *    initial_states, out, final_states, states and the workspace exactly as for
+ *    ssd_fused_state_fwd, except that fused.in.dt, fused.in.dA_cumsum and their strides are
+ *    ignored: the state kernel uses cumsum.dt_out / cumsum.dA_cumsum.  All four outputs carry
+ *    the same bits as the two separate calls would give.
+ *
+ *    When the tcgen05 kernel takes the problem and the raw dt has contiguous heads (16-bit or
+ *    fp32, each position's pair of heads aligned to its size), ONE launch does everything:
+ *    the persistent kernel computes each chunk's cumulative sums in the warp that needs them
+ *    for the B scaling and writes dt_out / dA_cumsum as a by-product.  Otherwise the call
+ *    enqueues the cumsum kernel and then the state kernels.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  ssd_chunk_cumsum_params_t cumsum;
+  ssd_fused_state_params_t fused;
+} ssd_state_path_params_t;
+
+SSD_API size_t ssd_state_path_workspace_bytes(const ssd_state_path_params_t* prm);
+SSD_API int ssd_state_path_fwd(const ssd_state_path_params_t* prm, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * 4b. ssd_fused_state_fwd without a caller-supplied workspace.  It has no counterpart in
  *    the reference (whose wrappers allocate with torch.empty / torch.zeros on every call,
  *    kernels/fused_concurrent.py:270-298).

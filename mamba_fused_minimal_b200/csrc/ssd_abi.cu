@@ -199,6 +199,52 @@ int ssd_fused_state_fwd(const ssd_fused_state_params_t* prm, ssd_stream_t stream
   return launch_state_passing(sp, st);
 }
 
+// The fused parameters of a state-path call with dt / dA_cumsum pointing at the cumsum outputs.
+static ssd_fused_state_params_t state_path_fused(const ssd_state_path_params_t& p) {
+  ssd_fused_state_params_t f = p.fused;
+  const ssd_chunk_cumsum_params_t& c = p.cumsum;
+  const int64_t L = c.chunk_size, nchunks = L > 0 ? (c.seqlen + L - 1) / L : 0;
+  f.in.dt = c.dt_out;
+  f.in.dA_cumsum = c.dA_cumsum;
+  f.in.chunk_size = c.chunk_size;
+  const int64_t strides[4] = {(int64_t)c.nheads * nchunks * L, nchunks * L, L, 1};
+  for (int i = 0; i < 4; ++i) f.in.dt_stride[i] = f.in.dA_stride[i] = strides[i];
+  return f;
+}
+
+size_t ssd_state_path_workspace_bytes(const ssd_state_path_params_t* prm) {
+  if (prm == nullptr) return 0;
+  const ssd_fused_state_params_t f = state_path_fused(*prm);
+  return ssd_fused_state_workspace_bytes(&f);
+}
+
+int ssd_state_path_fwd(const ssd_state_path_params_t* prm, ssd_stream_t stream) {
+  SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
+  const ssd_chunk_cumsum_params_t& c = prm->cumsum;
+  SSD_REQUIRE(c.dt && c.A && c.dt_out && c.dA_cumsum, SSD_ERR_BAD_ARGUMENT, "dt, A, dt_out and dA_cumsum must not be NULL");
+  SSD_REQUIRE(valid_dtype(c.dt_dtype) && valid_dtype(c.A_dtype) && (c.dt_bias == nullptr || valid_dtype(c.bias_dtype)),
+              SSD_ERR_BAD_ARGUMENT, "bad dtype");
+  const ssd_fused_state_params_t f = state_path_fused(*prm);
+  SSD_REQUIRE(c.batch == f.in.batch && c.seqlen == f.in.seqlen && c.nheads == f.in.nheads && c.chunk_size > 0,
+              SSD_ERR_BAD_ARGUMENT, "cumsum and state parameters disagree on batch / seqlen / nheads");
+  int rc = check_state_inputs(f.in);
+  if (rc != SSD_OK) return rc;
+  if (use_fast(f) && fused_raw_ok(f, c)) {
+    SSD_REQUIRE(f.out && f.final_states, SSD_ERR_BAD_ARGUMENT, "out and final_states must not be NULL");
+    SSD_REQUIRE(valid_dtype(f.out_dtype) && (f.initial_states == nullptr || valid_dtype(f.init_dtype)) &&
+                    (f.states == nullptr || valid_dtype(f.states_dtype)),
+                SSD_ERR_BAD_ARGUMENT, "bad dtype");
+    SSD_REQUIRE(f.workspace != nullptr && (reinterpret_cast<uintptr_t>(f.workspace) & 255) == 0, SSD_ERR_WORKSPACE,
+                "workspace is NULL or not 256-byte aligned");
+    SSD_REQUIRE(f.workspace_bytes >= ssd_fused_state_workspace_bytes(&f), SSD_ERR_WORKSPACE,
+                "workspace holds %zu bytes, %zu needed", f.workspace_bytes, ssd_fused_state_workspace_bytes(&f));
+    return launch_fused_fast(f, 0, reinterpret_cast<cudaStream_t>(stream), &c);
+  }
+  rc = ssd_chunk_cumsum_fwd(&c, stream);
+  if (rc != SSD_OK) return rc;
+  return ssd_fused_state_fwd(&f, stream);
+}
+
 void ssd_debug_set_wait_limit_cycles(long long cycles) {
   g_wait_limit_cycles.store(cycles > 0 ? cycles : 4000000000ll, std::memory_order_relaxed);
 }

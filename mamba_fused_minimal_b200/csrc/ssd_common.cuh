@@ -90,4 +90,36 @@ __device__ __forceinline__ float softplus_ref(float x) {
   return x <= 20.0f ? __logf(fast_exp(x) + 1.0f) : x;
 }
 
+// dt' of one position: bias, optional softplus, clamp (kernels/ssd_chunk_state.py:66-73 of the
+// reference).  One function for every kernel that produces dt', so that they agree bit for bit.
+__device__ __forceinline__ float dt_transform(float raw, float bias, bool softplus, float lo, float hi) {
+  float t = raw + bias;
+  if (softplus) t = softplus_ref(t);
+  return fminf(fmaxf(t, lo), hi);
+}
+
+// Inclusive running sum of d[i] * a over the 256 positions a warp holds as 8 consecutive ones
+// per lane (position = 8 * lane + i), continued from `carry`: each lane scans its eight
+// serially, the lane totals go through one shuffle scan.  s receives the sums; the return value
+// is `carry` plus the total, for the next 256 positions.  Shared by the cumsum kernel and the
+// state kernel that computes the cumulative sums itself: same operations, same order.
+__device__ __forceinline__ float warp_cumsum8(const float (&d)[8], float a, float carry, int lane, float (&s)[8]) {
+  float run = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    run += d[i] * a;
+    s[i] = run;
+  }
+  float incl = run;                                 // inclusive scan of the lane totals
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += t;
+  }
+  const float before = carry + (incl - run);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] += before;
+  return carry + __shfl_sync(0xffffffffu, incl, 31);
+}
+
 }  // namespace ssd

@@ -35,6 +35,14 @@
 //                         written with tcgen05.st to the head's A slot in tensor memory
 // The accumulator of a chunk is complete after its last stage; up to NBUF chunks of MMAs run
 // ahead of the epilogue.
+//
+// RAW variant (the whole state path in one launch): the kernel is given the raw dt, A and
+// dt_bias instead of dt_out / dA_cumsum.  The scale-vector warp then does the chunk cumsum of
+// kernels/ssd_chunk_state.py:65-79 itself -- per chunk and head it fetches the raw dt values
+// (small asynchronous copies, two chunks ahead), applies bias / softplus / clamp / tail mask,
+// scans dt * A with the same warp scan as the stand-alone cumsum kernel (so the results carry
+// the same bits), writes the dt_out and dA_cumsum rows as a by-product and derives the
+// per-position factors from the values it holds in registers.
 #include <cuda.h>
 
 #include <mutex>
@@ -63,7 +71,7 @@ template <int HPC>
 struct Cfg {
   static constexpr int NS = 6;                        // shared-memory stages (raw B tile + x tiles)
   static constexpr int NA = 2;                        // scaled-B (A operand) slots per head in TMEM
-  static constexpr int ND = 2;                        // dt/dA row slots
+  static constexpr int ND = 3;                        // dt/dA row slots (RAW variant: raw dt tiles)
   static constexpr int NBUF = (HPC == 2) ? 3 : 4;     // TMEM accumulators per head
   static constexpr int EPI_WARPS = 4 * HPC;
   // B-scaling warps: a warp can only write the TMEM lanes of its quadrant (warp index % 4), so
@@ -90,7 +98,8 @@ struct Cfg {
   // shared-memory map (byte offsets from a 1024-aligned base)
   static constexpr int OFF_STAGES = 0;
   static constexpr int OFF_DTDA = OFF_STAGES + NS * STAGE_BYTES;
-  static constexpr int DTDA_SLOT = HPC * 2 * kMaxL * 4;
+  // dt and dA_cumsum rows of every head -- or, in the RAW variant, one [kMaxL][16 bytes] tile of raw dt
+  static constexpr int DTDA_SLOT = (HPC * 2 * kMaxL * 4 > kMaxL * 16) ? HPC * 2 * kMaxL * 4 : kMaxL * 16;
   static constexpr int OFF_SCALE = OFF_DTDA + ND * DTDA_SLOT;
   static constexpr int SCALE_SLOT = HPC * kMaxL * 4;
   static constexpr int OFF_BARS = OFF_SCALE + 2 * SCALE_SLOT;
@@ -99,7 +108,8 @@ struct Cfg {
   static constexpr int B_EMPTY = B_FULL + NS;            // [NS]  stage consumed (one commit per MMA issuer)
   static constexpr int B_BS = B_EMPTY + NS;              // [NA]  scaled B written (one arrival per scaling warp)
   static constexpr int B_DD = B_BS + NA;                 // [ND]  dt / dA rows loaded
-  static constexpr int B_ACCF = B_DD + ND;               // [HPC][NBUF] accumulator complete
+  static constexpr int B_DDE = B_DD + ND;                // [ND]  RAW variant: raw dt tile consumed
+  static constexpr int B_ACCF = B_DDE + ND;              // [HPC][NBUF] accumulator complete
   static constexpr int B_ACCE = B_ACCF + HPC * NBUF;     // [HPC][NBUF] accumulator drained (4 epilogue warps)
   static constexpr int B_SCR = B_ACCE + HPC * NBUF;      // [2]   scale vector ready
   static constexpr int B_SCF = B_SCR + 2;                // [2]   scale vector no longer needed
@@ -109,7 +119,12 @@ struct Cfg {
   // staging for 16-bit passed states: every epilogue warp owns 32 rows (p) x 32 columns (its
   // dstate quadrant) = 32 x 64 bytes, laid out as a TMA box with the 64-byte swizzle
   static constexpr int STAGING_BYTES = 32 * 64;
-  static constexpr int OFF_STAGING = (OFF_CTL + 64 + 1023) / 1024 * 1024;
+  // RAW variant: each chunk's total log-decay travels from the scale-vector warp to the epilogue
+  // through a ring of RING entries per head (the epilogue lags by fewer chunks than that: two
+  // scale vectors, the A slots and NBUF accumulators)
+  static constexpr int RING = 8;
+  static constexpr int OFF_RING = OFF_CTL + 64;
+  static constexpr int OFF_STAGING = (OFF_RING + RING * HPC * 4 + 1023) / 1024 * 1024;
   static constexpr int SMEM_BYTES = OFF_STAGING + EPI_WARPS * STAGING_BYTES + 1024;   // + alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
   // Register budget per role (setmaxnreg).  The CTA is launched with LAUNCH_REGS per thread,
@@ -120,7 +135,7 @@ struct Cfg {
   static constexpr int LAUNCH_REGS = 65536 / (WARPS * 32) / 8 * 8;
   static constexpr int REGS_EPI = (HPC == 2) ? 144 : 168;
   static constexpr int REGS_SCALE = (HPC == 2) ? 72 : 96;
-  static constexpr int REGS_SERVICE = 40;
+  static constexpr int REGS_SERVICE = (HPC == 2) ? 48 : 64;   // the cumsum of the RAW variant runs here
   static constexpr bool REBALANCE = true;
   static_assert(EPI_WARPS * REGS_EPI + SERVICE_WARPS * REGS_SERVICE + SCALE_WARPS * REGS_SCALE <= WARPS * LAUNCH_REGS,
                 "per-role register counts exceed the launch allocation");
@@ -148,6 +163,15 @@ struct FusedArgs {
   int mode;               // 0: state passing fused; 1: per-chunk states only
   int defer;              // non-zero: segments that start inside a strip start from zero; the
                           // carried state is added afterwards by segment_fixup_kernel
+  // RAW variant: dt / dA above are OUTPUTS ((b, h, c, L) fp32 rows, written by the kernel), computed from
+  const void* dt_raw;     // (b, l, h) of raw_dtype, heads contiguous
+  const void* A;          // (h,)
+  const void* bias;       // (h,) or NULL
+  int64_t raw_s[2];       // b, l strides of dt_raw (elements)
+  int64_t A_stride, bias_stride;
+  int raw_dtype, A_dtype, bias_dtype;
+  int softplus;
+  float dt_min, dt_max;
   int debug;              // test hooks (ssd_debug_set_flags); 0 in normal use
   long long wait_limit;   // SM cycles a device-side wait may last
 };
@@ -210,10 +234,11 @@ template <> struct Pack<__half> {
   }
 };
 
-template <typename T, int HPC, bool OUT32, bool SEQ>
+template <typename T, int HPC, bool OUT32, bool SEQ, bool RAW>
 __global__ void __launch_bounds__(Cfg<HPC>::THREADS, 1)
 fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_B,
-                   const __grid_constant__ CUtensorMap tmap_out, const FusedArgs a) {
+                   const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_dt,
+                   const FusedArgs a) {
   using C = Cfg<HPC>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -229,6 +254,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   auto bar_empty = [&](int s) { return bars + 8u * (C::B_EMPTY + s); };
   auto bar_bs_full = [&](int t) { return bars + 8u * (C::B_BS + t); };
   auto bar_dd_full = [&](int r) { return bars + 8u * (C::B_DD + r); };
+  auto bar_dd_empty = [&](int r) { return bars + 8u * (C::B_DDE + r); };
   auto bar_acc_full = [&](int hd, int b) { return bars + 8u * (C::B_ACCF + hd * C::NBUF + b); };
   auto bar_acc_empty = [&](int hd, int b) { return bars + 8u * (C::B_ACCE + hd * C::NBUF + b); };
   auto bar_sc_ready = [&](int i) { return bars + 8u * (C::B_SCR + i); };
@@ -241,7 +267,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   if (tid == 0) {
     for (int s = 0; s < C::NS; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), HPC); }
     for (int t = 0; t < C::NA; ++t) mbar_init(bar_bs_full(t), C::SCALE_WARPS);
-    for (int r = 0; r < C::ND; ++r) mbar_init(bar_dd_full(r), 1);
+    for (int r = 0; r < C::ND; ++r) { mbar_init(bar_dd_full(r), 1); mbar_init(bar_dd_empty(r), 1); }
     for (int hd = 0; hd < HPC; ++hd)
       for (int b = 0; b < C::NBUF; ++b) { mbar_init(bar_acc_full(hd, b), 1); mbar_init(bar_acc_empty(hd, b), 4); }
     // group barriers take ONE arrival per warp: arrivals on one mbarrier serialise
@@ -260,6 +286,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_B);
     if (!OUT32 && a.mode == 0) prefetch_tensormap(&tmap_out);
+    if (RAW) prefetch_tensormap(&tmap_dt);
   }
   tc_fence_before();
   __syncthreads();
@@ -285,6 +312,26 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         const uint64_t keep = l2_policy_evict_normal(), stream_once = l2_policy_evict_first();
         uint32_t it = 0;
         bool ok = true;
+        // RAW variant: the raw dt tile of chunk i + 1 (the 16 bytes of heads around this CTA's heads x
+        // one chunk of positions, a tile [position][16 bytes]) is requested when chunk i starts; a slot
+        // is reused once the cumsum warp has read it
+        uint32_t ditem = 0;                                    // next raw dt tile to request
+        int pj = 0, pstrip = 0, pc = 0, pc1 = 0;
+        if (RAW && rg.m > 0) get_segment(rg, nchunks, 0, pstrip, pc, pc1);
+        auto fetch_raw = [&]() {
+          if (pj >= rg.m) return true;
+          const int slot = ditem % C::ND;
+          if (!mbar_wait(bar_dd_empty(slot), ((ditem / C::ND) & 1) ^ 1, wc, kWaitDdEmpty)) return false;
+          const int es = a.raw_dtype == SSD_F32 ? 4 : 2;
+          const int pb = pstrip / a.strips_per_batch;
+          const int ph0 = (pstrip % a.strips_per_batch) * HPC;
+          mbar_expect_tx(bar_dd_full(slot), L * 16);
+          tma_load_3d(sbase + C::OFF_DTDA + slot * C::DTDA_SLOT, &tmap_dt, bar_dd_full(slot), ph0 & ~(16 / es - 1), pc * L, pb);
+          ++ditem;
+          if (++pc >= pc1 && ++pj < rg.m) get_segment(rg, nchunks, pj, pstrip, pc, pc1);
+          return true;
+        };
+        if (RAW) ok = fetch_raw();
         for (int j = 0; j < rg.m && ok; ++j) {
           int strip, c0, c1;
           get_segment(rg, nchunks, j, strip, c0, c1);
@@ -292,6 +339,10 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           const int h0 = (strip % a.strips_per_batch) * HPC;
           const int g = h0 / ratio;
           for (int c = c0; c < c1 && ok; ++c) {
+            if (RAW) {
+              ok = fetch_raw();
+              if (!ok) break;
+            }
             const int limit = min(L, a.seqlen - c * L);
             const int ksteps = (limit + kKT - 1) / kKT;
             for (int ks = 0; ks < ksteps; ++ks, ++it) {
@@ -353,6 +404,117 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             }
             if (ok) mma_commit(bar_acc_full(mhd, buf));
           }
+        }
+      }
+    } else if (warp == C::EPI_WARPS + 3 && RAW) {
+      // ============================== chunk cumsum + scale vectors ====================
+      // One TMA copy per chunk (issued by the producer warp, one chunk ahead) brings the raw dt of the
+      // 16-byte group of heads that holds this CTA's heads (4 fp32 or 8 sixteen-bit values per position)
+      // as a tile [position][16 bytes].
+      // Phase A, lane = position modulo 32: bias / softplus / clamp / tail mask
+      // (kernels/ssd_chunk_state.py:66-74), dt' parked in the scale-vector slot ([head][position]).
+      // Phase B, lane = 8 consecutive positions: cumulative sum of dt' * A with the cumsum kernel's
+      // warp scan (same operations, same order, same bits), the dt_out / dA_cumsum rows written to
+      // global memory, the factors exp(min(a_last - a_k, 0)) * dt_k written over the parked dt', and
+      // the chunk's total left for the epilogue.
+      const int es = a.raw_dtype == SSD_F32 ? 4 : 2;
+      const int hmask = 16 / es - 1;                               // heads per 16-byte group, minus one
+      const bool sp = a.softplus != 0;
+      // the clamp is the identity for the default limits once the softplus has made dt' non-negative
+      const bool clamp = !(sp && a.dt_min <= 0.0f && a.dt_max == __int_as_float(0x7f800000));
+      uint32_t item = 0;
+      bool ok = true;
+      for (int j = 0; j < rg.m && ok; ++j) {
+        int strip, c0, c1;
+        get_segment(rg, nchunks, j, strip, c0, c1);
+        const int b = strip / a.strips_per_batch;
+        const int h0 = (strip % a.strips_per_batch) * HPC;
+        float Ah[HPC], bh[HPC];
+#pragma unroll
+        for (int hd = 0; hd < HPC; ++hd) {
+          Ah[hd] = load_f(a.A, a.A_dtype, (int64_t)(h0 + hd) * a.A_stride);
+          bh[hd] = a.bias != nullptr ? load_f(a.bias, a.bias_dtype, (int64_t)(h0 + hd) * a.bias_stride) : 0.0f;
+        }
+        const uint32_t in_group = (uint32_t)(h0 & hmask) * es;      // byte offset of head h0 inside a position's 16 bytes
+        // element offset of (b, h0, chunk 0, position 8 * lane) in the two fp32 outputs
+        const int64_t row0 = (int64_t)b * a.dt_s[0] + (int64_t)h0 * a.dt_s[1] + lane * 8;
+        const int k0 = lane * 8;
+        for (int c = c0; c < c1 && ok; ++c, ++item) {
+          const int r = item % C::ND;
+          ok = mbar_wait(bar_dd_full(r), (item / C::ND) & 1, wc, kWaitDdFull);
+          if (!ok) break;
+          if (item >= 2) {
+            ok = mbar_wait(bar_sc_free(item & 1), ((item >> 1) - 1) & 1, wc, kWaitGroup);
+            if (!ok) break;
+          }
+          const uint32_t rawp = sbase + C::OFF_DTDA + r * C::DTDA_SLOT + in_group;
+          const uint32_t scp = sbase + C::OFF_SCALE + (item & 1) * C::SCALE_SLOT;
+          const int limit = min(L, a.seqlen - c * L);
+          // ---- phase A (two positions per head in flight: four independent chains)
+#pragma unroll 2
+          for (int kk = 0; kk < kMaxL / 32; ++kk) {
+            const int k = kk * 32 + lane;
+            if (k >= L) break;
+            float v[HPC];
+            if (a.raw_dtype == SSD_F32) {
+              if (HPC == 2) lds_v2(rawp + k * 16, v[0], v[HPC - 1]);
+              else v[0] = lds_f32(rawp + k * 16);
+            } else {
+              const uint32_t w = HPC == 2 ? lds_u32(rawp + k * 16) : (uint32_t)lds_u16(rawp + k * 16);
+              if (a.raw_dtype == SSD_BF16) {
+                v[0] = __uint_as_float(w << 16);
+                if (HPC == 2) v[HPC - 1] = __uint_as_float(w & 0xffff0000u);
+              } else {
+                const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w));
+                v[0] = f2.x;
+                if (HPC == 2) v[HPC - 1] = f2.y;
+              }
+            }
+#pragma unroll
+            for (int hd = 0; hd < HPC; ++hd) {
+              float t = v[hd] + bh[hd];
+              if (sp) t = softplus_ref(t);
+              if (clamp) t = fminf(fmaxf(t, a.dt_min), a.dt_max);
+              sts_f32(scp + (hd * kMaxL + k) * 4, k < limit ? t : 0.0f);    // positions past the sequence hold zeros
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_dd_empty(r));     // the raw tile has been read
+          // ---- phase B
+#pragma unroll
+          for (int hd = 0; hd < HPC; ++hd) {
+            float d[8], cs[8];
+            if (k0 < L) {
+              lds_v4(scp + (hd * kMaxL + k0) * 4, d[0], d[1], d[2], d[3]);
+              lds_v4(scp + (hd * kMaxL + k0 + 4) * 4, d[4], d[5], d[6], d[7]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) d[i] = 0.0f;
+            }
+            warp_cumsum8(d, Ah[hd], 0.0f, lane, cs);
+            // the chunk's total: the sum at position L - 1 (flat over a ragged tail); L is a multiple of 64
+            const float last = __shfl_sync(0xffffffffu, cs[7], (L - 1) >> 3);
+            if (k0 < L) {
+              const int64_t row = row0 + (int64_t)hd * a.dt_s[1] + (int64_t)c * a.dt_s[2];
+              float4* o1 = reinterpret_cast<float4*>(const_cast<float*>(a.dt) + row);
+              float4* o2 = reinterpret_cast<float4*>(const_cast<float*>(a.dA) + row);
+              o1[0] = make_float4(d[0], d[1], d[2], d[3]);
+              o1[1] = make_float4(d[4], d[5], d[6], d[7]);
+              o2[0] = make_float4(cs[0], cs[1], cs[2], cs[3]);
+              o2[1] = make_float4(cs[4], cs[5], cs[6], cs[7]);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float dl = last - cs[i];
+                if (a.clamp_decay) dl = fminf(dl, 0.0f);
+                d[i] = fast_exp(dl) * d[i];
+              }
+              sts_v4(scp + (hd * kMaxL + k0) * 4, d[0], d[1], d[2], d[3]);
+              sts_v4(scp + (hd * kMaxL + k0 + 4) * 4, d[4], d[5], d[6], d[7]);
+            }
+            if (lane == 0) sts_f32(sbase + C::OFF_RING + ((item % C::RING) * HPC + hd) * 4, last);
+          }
+          __syncwarp();                       // every lane has written its factors
+          if (lane == 0) mbar_arrive(bar_sc_ready(item & 1));
         }
       }
     } else if (warp == C::EPI_WARPS + 3) {
@@ -625,7 +787,7 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       for (int c = c0; c < c1 && ok; ++c, ++item) {
         const int buf = item % C::NBUF;
         float decay = 0.0f;
-        if (a.mode == 0) {
+        if (a.mode == 0 && !RAW) {
           decay = fast_exp(__ldg(a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2] + (L - 1)));
           if constexpr (SEQ) {
             const int seq_new = sq[(int64_t)(min((c + 1) * L, a.seqlen) - 1) * a.seq_s[1]];
@@ -636,6 +798,11 @@ fused_state_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         ok = mbar_wait(bar_acc_full(hd, buf), (item / C::NBUF) & 1, wc, kWaitAccFull, 128);
         if (!ok) break;
         tc_fence_after();
+        if constexpr (RAW) {
+          // written by the scale-vector warp before it released this chunk's factors; the chain of
+          // barriers from there to this accumulator orders the read
+          decay = fast_exp(reinterpret_cast<const volatile float*>(smem + C::OFF_RING)[(item % C::RING) * HPC + hd]);
+        }
         const uint32_t taddr = tmem_base + lane_sel + (hd * C::NBUF + buf) * kP;
 #pragma unroll
         for (int hq = 0; hq < 2; ++hq) {
@@ -867,6 +1034,26 @@ int make_out_map(CUtensorMap* map, void* base, int dtype, int nheads, int nchunk
   return SSD_OK;
 }
 
+// Raw dt (b, l, h) with contiguous heads as a 3-D map (h, l, b); box = the 16 bytes of heads around
+// the CTA's heads x one chunk of positions, no swizzle: a tile [position][16 bytes].
+int make_dt_map(CUtensorMap* map, const void* base, int dtype, int nheads, int seqlen, int batch, int64_t stride_l,
+                int64_t stride_b, int chunk_size) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const int es = dtype_size(dtype);
+  const cuuint64_t dims[3] = {(cuuint64_t)nheads, (cuuint64_t)seqlen, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)stride_l * es, (cuuint64_t)stride_b * es};
+  const cuuint32_t box[3] = {(cuuint32_t)(16 / es), (cuuint32_t)chunk_size, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == SSD_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled (dt) failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int num_sms() {
@@ -883,7 +1070,8 @@ int num_sms() {
 }
 
 template <typename T, int HPC>
-int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream) {
+int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream,
+                   const ssd_chunk_cumsum_params_t* raw) {
   using C = Cfg<HPC>;
   const ssd_state_inputs_t& in = p.in;
   CUtensorMap mx, mB;
@@ -941,6 +1129,21 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   a.states_dtype = p.states_dtype;
   a.clamp_decay = p.clamp_decay;
   a.mode = mode;
+  if (raw != nullptr) {
+    a.dt_raw = raw->dt;
+    a.A = raw->A;
+    a.bias = raw->dt_bias;
+    a.raw_s[0] = raw->dt_stride_b;
+    a.raw_s[1] = raw->dt_stride_l;
+    a.A_stride = raw->A_stride;
+    a.bias_stride = raw->bias_stride;
+    a.raw_dtype = raw->dt_dtype;
+    a.A_dtype = raw->A_dtype;
+    a.bias_dtype = raw->bias_dtype;
+    a.softplus = raw->dt_softplus;
+    a.dt_min = raw->dt_min;
+    a.dt_max = raw->dt_max;
+  }
   a.debug = debug_flags();
   a.wait_limit = wait_limit_cycles();
 
@@ -948,8 +1151,10 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
   const bool out32 = p.out_dtype == SSD_F32 && mode == 0;
   const bool seq = in.seq_idx != nullptr;
-  auto kern = out32 ? (seq ? fused_state_kernel<T, HPC, true, true> : fused_state_kernel<T, HPC, true, false>)
-                    : (seq ? fused_state_kernel<T, HPC, false, true> : fused_state_kernel<T, HPC, false, false>);
+  SSD_REQUIRE(raw == nullptr || (!seq && mode == 0), SSD_ERR_UNSUPPORTED, "raw dt with seq_idx or in the states-only mode");
+  auto kern = out32 ? (seq ? fused_state_kernel<T, HPC, true, true, false> : fused_state_kernel<T, HPC, true, false, false>)
+                    : (seq ? fused_state_kernel<T, HPC, false, true, false> : fused_state_kernel<T, HPC, false, false, false>);
+  if (raw != nullptr) kern = out32 ? fused_state_kernel<T, HPC, true, false, true> : fused_state_kernel<T, HPC, false, false, true>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   // A strip longer than a CTA's range would make the CTAs of that strip wait for one another
   // in turn; then the carry is deferred to a second, small kernel instead.
@@ -958,7 +1163,13 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   const long long per_cta = (total + grid - 1) / grid;
   // (not with packed sequences: the second pass multiplies decays across a cut and knows nothing of resets)
   a.defer = (mode == 0 && a.nchunks > per_cta && per_cta >= 16 && in.seq_idx == nullptr) ? 1 : 0;
-  kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(mx, mB, mo, a);
+  CUtensorMap mdt = mx;                 // a valid map even where the kernel never touches it
+  if (raw != nullptr) {
+    rc = make_dt_map(&mdt, raw->dt, raw->dt_dtype, in.nheads, in.seqlen, in.batch, raw->dt_stride_l, raw->dt_stride_b,
+                     in.chunk_size);
+    if (rc != SSD_OK) return rc;
+  }
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(mx, mB, mo, mdt, a);
   SSD_CUDA_OK(cudaGetLastError());
   if (a.defer) {
     SegFixArgs f{};
@@ -1087,13 +1298,40 @@ size_t fused_fast_workspace_bytes(const ssd_fused_state_params_t&) {
 }
 
 
-int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream) {
+int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream,
+                      const ssd_chunk_cumsum_params_t* raw) {
   const int variant = fused_fast_variant(p, nullptr);
   SSD_REQUIRE(variant != 0, SSD_ERR_UNSUPPORTED, "fused tcgen05 kernel cannot take this problem");
+  SSD_REQUIRE(raw == nullptr || fused_raw_ok(p, *raw), SSD_ERR_UNSUPPORTED,
+              "fused tcgen05 kernel cannot compute the cumsum of this dt itself");
   const bool bf16 = p.in.in_dtype == SSD_BF16;
   if (variant == 2)
-    return bf16 ? launch_variant<__nv_bfloat16, 2>(p, mode, stream) : launch_variant<__half, 2>(p, mode, stream);
-  return bf16 ? launch_variant<__nv_bfloat16, 1>(p, mode, stream) : launch_variant<__half, 1>(p, mode, stream);
+    return bf16 ? launch_variant<__nv_bfloat16, 2>(p, mode, stream, raw) : launch_variant<__half, 2>(p, mode, stream, raw);
+  return bf16 ? launch_variant<__nv_bfloat16, 1>(p, mode, stream, raw) : launch_variant<__half, 1>(p, mode, stream, raw);
+}
+
+// The RAW variant fetches the raw dt with TMA: heads contiguous, base and the position / batch
+// strides multiples of 16 bytes.
+bool fused_raw_ok(const ssd_fused_state_params_t& p, const ssd_chunk_cumsum_params_t& raw) {
+  const int variant = fused_fast_variant(p, nullptr);
+  if (variant == 0 || p.in.seq_idx != nullptr) return false;
+  // Inside the persistent kernel the cumsum is one warp's work per CTA, which makes a chunk about 6 %
+  // slower than when a stand-alone cumsum kernel has run first; what the single launch saves is the
+  // second launch with its ramp and tail, a fixed 5 - 7 us.  Measured on B200 (Mamba2-130M layer shape
+  // 41 vs 48 us, 2.7B shape 120 vs 122 us, 8B-style shape 987 vs 897 us) the two meet at roughly a
+  // hundred chunks per CTA; beyond that the two launches are used.  The results are the same bits.
+  const long long nchunks = (p.in.seqlen + p.in.chunk_size - 1) / p.in.chunk_size;
+  const long long total = (long long)p.in.batch * (p.in.nheads / variant) * nchunks;
+  const long long grid = std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
+  if (grid > 0 && (total + grid - 1) / grid > 96) return false;
+  if (raw.dt_stride_h != 1) return false;
+  const int es = dtype_size(raw.dt_dtype);
+  if (reinterpret_cast<uintptr_t>(raw.dt) % 16 != 0) return false;
+  if ((raw.dt_stride_l * es) % 16 != 0 || (raw.dt_stride_b * es) % 16 != 0) return false;
+  if (raw.batch != p.in.batch || raw.seqlen != p.in.seqlen || raw.nheads != p.in.nheads ||
+      raw.chunk_size != p.in.chunk_size)
+    return false;
+  return true;
 }
 
 }  // namespace ssd

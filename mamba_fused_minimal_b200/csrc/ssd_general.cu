@@ -19,6 +19,7 @@ constexpr int CS_HT = 16;        // heads per block
 constexpr int CS_THREADS = 256;
 constexpr int CS_PER = 8;        // consecutive positions per lane in the scan
 constexpr int CS_ROUND = 32 * CS_PER;
+static_assert(CS_PER == 8, "warp_cumsum8 scans eight positions per lane");
 
 // 16 bytes of consecutive heads of one position, widened to fp32.
 template <typename DT> struct DtVec;
@@ -107,9 +108,7 @@ chunk_cumsum_kernel(ssd_chunk_cumsum_params_t p, int nchunks, int pitch, int vec
           const bool live = k < limit;
 #pragma unroll
           for (int j = 0; j < VEC; ++j) {
-            float t = v[u][j] + bias[j];
-            if (sp) t = softplus_ref(t);
-            t = fminf(fmaxf(t, lo), hi);
+            const float t = dt_transform(v[u][j], bias[j], sp, lo, hi);
             dst[j * pitch + k] = live ? t : 0.0f;      // positions past the chunk hold zeros
           }
         }
@@ -137,11 +136,7 @@ chunk_cumsum_kernel(ssd_chunk_cumsum_params_t p, int nchunks, int pitch, int vec
         const int k = k0 + u * kRowsPerPass;
         if (k < Lr) {
           float t = 0.0f;
-          if (head_ok && k < limit) {
-            t = v[u] + bias;
-            if (p.dt_softplus) t = softplus_ref(t);
-            t = fminf(fmaxf(t, p.dt_min), p.dt_max);
-          }
+          if (head_ok && k < limit) t = dt_transform(v[u], bias, p.dt_softplus != 0, p.dt_min, p.dt_max);
           tile[hh_t * pitch + k] = t;                    // positions past the chunk hold zeros
         }
       }
@@ -165,22 +160,7 @@ chunk_cumsum_kernel(ssd_chunk_cumsum_params_t p, int nchunks, int pitch, int vec
         d[0] = lo.x; d[1] = lo.y; d[2] = lo.z; d[3] = lo.w;
         d[4] = hi.x; d[5] = hi.y; d[6] = hi.z; d[7] = hi.w;
       }
-      float run = 0.0f;
-#pragma unroll
-      for (int i = 0; i < CS_PER; ++i) {
-        run += d[i] * a;
-        s[i] = run;
-      }
-      float incl = run;                                 // inclusive scan of the lane totals
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const float t = __shfl_up_sync(0xffffffffu, incl, off);
-        if (lane >= off) incl += t;
-      }
-      const float before = carry + (incl - run);
-#pragma unroll
-      for (int i = 0; i < CS_PER; ++i) s[i] += before;
-      carry += __shfl_sync(0xffffffffu, incl, 31);
+      carry = warp_cumsum8(d, a, carry, lane, s);
       if (vec && k + CS_PER <= L) {
         float4* o1 = reinterpret_cast<float4*>(p.dt_out + obase + k);
         float4* o2 = reinterpret_cast<float4*>(p.dA_cumsum + obase + k);

@@ -35,7 +35,11 @@ struct FusedWorkspaceLayout {
 int fused_fast_variant(const ssd_fused_state_params_t& p, const char** why);
 size_t fused_fast_workspace_bytes(const ssd_fused_state_params_t& p);
 // mode 0: chunk state + state passing; mode 1: per-chunk states only (p.states required).
-int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream);
+// raw != NULL: the RAW variant -- p.in.dt / p.in.dA_cumsum are OUTPUTS computed in the same launch
+// from the raw dt, A and dt_bias described by *raw (mode 0, no seq_idx; see fused_raw_ok).
+int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream,
+                      const ssd_chunk_cumsum_params_t* raw = nullptr);
+bool fused_raw_ok(const ssd_fused_state_params_t& p, const ssd_chunk_cumsum_params_t& raw);
 // Reads (and clears when set) the wait status word of launches in the states-only mode, which
 // have no workspace, on the current device; *code = 0 when no wait gave up.
 int states_only_wait_status(int* code);

@@ -287,6 +287,109 @@ std::tuple<Tensor, Tensor> fused_state_fwd(const Tensor& B, const Tensor& x, con
   return {out, fin};
 }
 
+// ssd_state_path_fwd: chunk cumsum + fused chunk state / state passing in one call (one launch
+// when the tcgen05 kernel takes the problem).  Returns (dA_cumsum, dt_out, out, final_states).
+std::tuple<Tensor, Tensor, Tensor, Tensor> state_path_fwd(
+    const Tensor& dt, const Tensor& A, const Tensor& B, const Tensor& x, int64_t chunk_size,
+    std::optional<at::ScalarType> out_dtype, const OptTensor& dt_bias, bool dt_softplus, double dt_min, double dt_max,
+    const OptTensor& initial_states, const OptTensor& seq_idx, const OptTensor& states_in, bool states_in_fp32,
+    bool clamp_decay, bool force_general, const OptTensor& final_out) {
+  TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor (libssd_b200 has no CPU path)");
+  check_cuda(dt, x, "dt");
+  check_cuda(A, x, "A");
+  check_cuda(B, x, "B");
+  TORCH_CHECK(dt.dim() == 3 && A.dim() == 1 && x.dim() == 4 && B.dim() == 4,
+              "dt must be (b, l, h), A (h,), x (b, l, h, p), B (b, l, g, n)");
+  TORCH_CHECK(B.scalar_type() == x.scalar_type(), "B and x must have the same dtype");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t batch = x.size(0), seqlen = x.size(1), nheads = x.size(2), headdim = x.size(3), dstate = B.size(3);
+  TORCH_CHECK(dt.size(0) == batch && dt.size(1) == seqlen && dt.size(2) == nheads && A.size(0) == nheads &&
+                  B.size(0) == batch && B.size(1) == seqlen,
+              "dt, A, B and x disagree on batch / seqlen / nheads");
+  const int64_t nchunks = (seqlen + chunk_size - 1) / chunk_size;
+  auto f32 = torch::dtype(torch::kFloat).device(x.device());
+  Tensor dt_out = torch::empty({batch, nheads, nchunks, chunk_size}, f32);
+  Tensor dA_cumsum = torch::empty({batch, nheads, nchunks, chunk_size}, f32);
+  ssd_state_path_params_t p{};
+  ssd_chunk_cumsum_params_t& c = p.cumsum;
+  c.dt = dt.data_ptr();
+  c.A = A.data_ptr();
+  c.dt_dtype = dtype_code(dt, "dt");
+  c.A_dtype = dtype_code(A, "A");
+  if (dt_bias.has_value()) {
+    check_cuda(*dt_bias, x, "dt_bias");
+    TORCH_CHECK(dt_bias->dim() == 1 && dt_bias->size(0) == nheads, "dt_bias must be (h,)");
+    c.dt_bias = dt_bias->data_ptr();
+    c.bias_dtype = dtype_code(*dt_bias, "dt_bias");
+    c.bias_stride = dt_bias->stride(0);
+  }
+  c.dt_out = dt_out.data_ptr<float>();
+  c.dA_cumsum = dA_cumsum.data_ptr<float>();
+  c.batch = batch;
+  c.seqlen = seqlen;
+  c.nheads = nheads;
+  c.chunk_size = chunk_size;
+  c.dt_stride_b = dt.stride(0);
+  c.dt_stride_l = dt.stride(1);
+  c.dt_stride_h = dt.stride(2);
+  c.A_stride = A.stride(0);
+  c.dt_min = static_cast<float>(dt_min);
+  c.dt_max = static_cast<float>(dt_max);
+  c.dt_softplus = dt_softplus ? 1 : 0;
+
+  ssd_fused_state_params_t& f = p.fused;
+  Tensor hold;
+  fill_state_inputs(f.in, B, x, dt_out, dA_cumsum, seq_idx, hold);
+  const at::ScalarType states_dt = states_in.has_value() ? states_in->scalar_type()
+                                                         : (states_in_fp32 ? at::kFloat : B.scalar_type());
+  const at::ScalarType odt = out_dtype.value_or(states_dt);
+  Tensor out = torch::empty({batch, nchunks, nheads, headdim, dstate}, torch::dtype(odt).device(x.device()));
+  Tensor fin;
+  if (final_out.has_value()) {
+    fin = *final_out;
+    check_cuda(fin, x, "final_states");
+    TORCH_CHECK(fin.scalar_type() == at::kFloat && fin.dim() == 4 && fin.size(0) == batch && fin.size(1) == nheads &&
+                    fin.size(2) == headdim && fin.size(3) == dstate && fin.stride(3) == 1,
+                "final_states must be fp32 (b, h, p, n) with a contiguous last dimension");
+  } else {
+    fin = torch::empty({batch, nheads, headdim, dstate}, f32);
+  }
+  if (initial_states.has_value()) {
+    check_cuda(*initial_states, x, "initial_states");
+    TORCH_CHECK(initial_states->dim() == 4 && initial_states->stride(3) == 1 && initial_states->size(0) == batch &&
+                    initial_states->size(1) == nheads && initial_states->size(2) == headdim &&
+                    initial_states->size(3) == dstate,
+                "initial_states must be (b, h, p, n) with a contiguous last dimension");
+    f.initial_states = initial_states->data_ptr();
+    f.init_dtype = dtype_code(*initial_states, "initial_states");
+    copy_strides(f.init_stride, *initial_states, {0, 1, 2});
+  }
+  if (states_in.has_value()) {
+    check_cuda(*states_in, x, "states");
+    TORCH_CHECK(states_in->dim() == 5 && states_in->stride(4) == 1 && states_in->size(0) == batch &&
+                    states_in->size(1) == nchunks && states_in->size(2) == nheads && states_in->size(3) == headdim &&
+                    states_in->size(4) == dstate,
+                "states must be (b, c, h, p, n) with a contiguous last dimension");
+    f.states = states_in->data_ptr();
+    f.states_dtype = dtype_code(*states_in, "states");
+    copy_strides(f.states_stride, *states_in, {0, 1, 2, 3});
+  }
+  f.out = out.data_ptr();
+  f.out_dtype = dtype_code(odt);
+  copy_strides(f.out_stride, out, {0, 1, 2, 3});
+  f.final_states = fin.data_ptr<float>();
+  copy_strides(f.final_stride, fin, {0, 1, 2});
+  f.clamp_decay = clamp_decay ? 1 : 0;
+  f.force_general = force_general ? 1 : 0;
+  const size_t need = ssd_state_path_workspace_bytes(&p);
+  const ssd_stream_t stream = current_stream(x);
+  Tensor ws = get_workspace(x, need, stream);
+  f.workspace = ws.data_ptr();
+  f.workspace_bytes = ws.numel();
+  check_rc(ssd_state_path_fwd(&p, stream), "ssd_state_path_fwd");
+  return {dA_cumsum, dt_out, out, fin};
+}
+
 // ssd_fused_state_fwd_static: the caller brings `out` and `final_states`; nothing is
 // allocated here or in the library (the scratch is the library's own static device array).
 void fused_state_fwd_static(const Tensor& B, const Tensor& x, const Tensor& dt, const Tensor& dA_cumsum,
@@ -534,6 +637,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out_dtype") = py::none(), py::arg("initial_states") = py::none(), py::arg("seq_idx") = py::none(),
         py::arg("states") = py::none(), py::arg("states_in_fp32") = true, py::arg("clamp_decay") = true,
         py::arg("force_general") = false, py::arg("final_states") = py::none());
+  m.def("state_path_fwd", &state_path_fwd, py::arg("dt"), py::arg("A"), py::arg("B"), py::arg("x"), py::arg("chunk_size"),
+        py::arg("out_dtype") = py::none(), py::arg("dt_bias") = py::none(), py::arg("dt_softplus") = false,
+        py::arg("dt_min") = 0.0, py::arg("dt_max") = std::numeric_limits<double>::infinity(),
+        py::arg("initial_states") = py::none(), py::arg("seq_idx") = py::none(), py::arg("states") = py::none(),
+        py::arg("states_in_fp32") = true, py::arg("clamp_decay") = true, py::arg("force_general") = false,
+        py::arg("final_states") = py::none());
   m.def("fused_state_fwd_static", &fused_state_fwd_static, py::arg("B"), py::arg("x"), py::arg("dt"),
         py::arg("dA_cumsum"), py::arg("out"), py::arg("final_states"), py::arg("initial_states") = py::none(),
         py::arg("states") = py::none(), py::arg("clamp_decay") = true, py::arg("force_general") = false);

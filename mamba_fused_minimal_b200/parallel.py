@@ -94,6 +94,28 @@ def carry_in_state(Z_all, logP_all, rank):
     return s_in
 
 
+def seqpar_state_path_fwd(dt, A, B, x, chunk_size, out_dtype, dt_bias=None, dt_softplus=False,
+                          dt_limit=(0.0, float("inf")), initial_states=None, group=None):
+    """Sequence-parallel form of `_state_path_fwd`: chunk cumsum, local scan, exchange and fix-up
+    from this rank's slice of the raw dt.  Returns (dA_cumsum, dt_out, out, final) for the slice."""
+    from ._ext import C
+    from .kernels.state_path import _state_path_fwd
+    rank = dist.get_rank(group)
+    init = initial_states if rank == 0 else None
+    batch, _, nheads, headdim = x.shape
+    dstate = B.shape[-1]
+    buf, Z, logP = summary_buffer(batch, nheads, headdim, dstate, x.device)
+    dA_cumsum, dt_out, out, _ = _state_path_fwd(dt, A, B, x, chunk_size, out_dtype, dt_bias=dt_bias,
+                                                dt_softplus=dt_softplus, dt_limit=dt_limit, initial_states=init,
+                                                final_states=Z)
+    dA_last = dA_cumsum[:, :, :, -1]
+    torch.sum(dA_last, dim=-1, out=logP)
+    Z_all, logP_all = exchange_summaries(buf, (batch, nheads, headdim, dstate), group)
+    if rank > 0:
+        C.seqpar_fixup(Z_all, logP_all, rank, dA_last, out, Z)      # Z becomes the state leaving the slice
+    return dA_cumsum, dt_out, out, Z
+
+
 def seqpar_fused_state_fwd(B, x, dt, dA_cumsum, out_dtype, initial_states=None, group=None):
     """Sequence-parallel form of the fused entry point.  Arguments are this rank's slice
     (dt, dA_cumsum from `_chunk_cumsum_fwd` on the slice); `initial_states` is honoured on rank
