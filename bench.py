@@ -230,6 +230,101 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def reference_triton_unfused(tree, w, dev):
+    """The reference's own Triton kernels on this GPU, the five UNFUSED ones (cumsum, chunk state,
+    state passing, chunk bmm, chunk scan; none of them spin-waits), imported from the reference tree at
+    `tree`, on the same seeded inputs, each timed by CUDA events (median of 20 after 5 warm-ups, which
+    also cover Triton's autotuning), with this library's kernels beside them and the fraction of
+    bit-equal outputs.  Returns a dict; {"unavailable": why} if Triton or the tree is missing."""
+    try:
+        import triton  # noqa: F401
+    except Exception as e:
+        return {"unavailable": f"triton is not importable: {e!r}"}
+    if not os.path.isdir(os.path.join(tree, "kernels")):
+        return {"unavailable": f"no kernels/ package under {tree}"}
+    sys.path.insert(0, os.path.abspath(tree))
+    try:
+        import kernels.ssd_bmm as r_bmm
+        import kernels.ssd_chunk_scan as r_scan
+        import kernels.ssd_chunk_state as r_cs
+        import kernels.ssd_state_passing as r_sp
+    except Exception as e:
+        return {"unavailable": f"the reference's kernels do not import: {e!r}"}
+    finally:
+        sys.path.pop(0)
+    import triton
+    from mamba_fused_minimal_b200.kernels.fused_concurrent import _fused_chunk_state_state_passing_fwd_concurrent as fused
+    from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
+    from mamba_fused_minimal_b200.kernels.ssd_bmm import _bmm_chunk_fwd as bmm
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _chunk_scan_fwd as scan
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_state import _chunk_cumsum_fwd as cumsum, _chunk_state_fwd as cstate
+    from mamba_fused_minimal_b200.kernels.ssd_state_passing import _state_passing_fwd as spass
+    from mamba_fused_minimal_b200.kernels.state_path import _state_path_fwd as state_path
+    b, l, h, p, g, n, L = (w[k] for k in ("batch", "seqlen", "nheads", "headdim", "ngroups", "dstate", "chunk_size"))
+    d = generate_benchmark_data(b, l, h, p, g, n, dtype=torch.bfloat16, device=dev, seed=0)
+    x, B, C, dt, A, bias, D = d["x"], d["B"], d["C"], d["dt"], d["A"], d["dt_bias"], d["D"].to(torch.bfloat16)
+
+    def med(fn, n_it=20, warm=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_it)]
+        for e0, e1 in ev:
+            e0.record()
+            fn()
+            e1.record()
+        torch.cuda.synchronize()
+        return statistics.median(e0.elapsed_time(e1) for e0, e1 in ev)
+
+    def same(a, r):
+        return float((a == r).float().mean().item())
+
+    res = {"triton": triton.__version__, "shape": {k: v for k, v in w.items() if k != "name"},
+           "timing": "CUDA events, median of 20 after 5 warm-ups; inputs (365 MB) exceed L2", "ms": {}, "parity": {}}
+    ms = res["ms"]
+    # cumsum
+    ms["ref_chunk_cumsum"] = med(lambda: r_cs._chunk_cumsum_fwd(dt, A, L, dt_bias=bias, dt_softplus=True))
+    ms["b200_chunk_cumsum"] = med(lambda: cumsum(dt, A, L, dt_bias=bias, dt_softplus=True))
+    r_dA, r_dt = r_cs._chunk_cumsum_fwd(dt, A, L, dt_bias=bias, dt_softplus=True)
+    m_dA, m_dt = cumsum(dt, A, L, dt_bias=bias, dt_softplus=True)
+    res["parity"]["dA_cumsum_max_abs_diff_over_max"] = float(((m_dA - r_dA).abs().max() / r_dA.abs().max()).item())
+    # the state kernels on the REFERENCE's dt / dA_cumsum, so that they see identical inputs
+    ms["ref_chunk_state"] = med(lambda: r_cs._chunk_state_fwd(B, x, r_dt, r_dA, states_in_fp32=True))
+    r_st = r_cs._chunk_state_fwd(B, x, r_dt, r_dA, states_in_fp32=True)
+    ms["ref_state_passing"] = med(lambda: r_sp._state_passing_fwd(r_st.flatten(-2), r_dA[:, :, :, -1], out_dtype=torch.bfloat16))
+    r_out, r_fin = r_sp._state_passing_fwd(r_st.flatten(-2), r_dA[:, :, :, -1], out_dtype=torch.bfloat16)
+    ms["b200_chunk_state"] = med(lambda: cstate(B, x, r_dt, r_dA))
+    m_st = cstate(B, x, r_dt, r_dA)
+    ms["b200_state_passing"] = med(lambda: spass(m_st.flatten(-2), r_dA[:, :, :, -1], out_dtype=torch.bfloat16))
+    ms["b200_fused_state"] = med(lambda: fused(B, x, r_dt, r_dA, torch.bfloat16))
+    ms["b200_state_path_one_call"] = med(lambda: state_path(dt, A, B, x, L, torch.bfloat16, dt_bias=bias, dt_softplus=True))
+    m_out, m_fin = fused(B, x, r_dt, r_dA, torch.bfloat16)
+    res["parity"]["chunk_states_max_abs_diff_over_max"] = float(((m_st - r_st).abs().max() / r_st.abs().max()).item())
+    res["parity"]["passed_states_bit_equal_fraction"] = same(m_out, r_out.view_as(m_out))
+    res["parity"]["final_states_bit_equal_fraction"] = same(m_fin, r_fin.view_as(m_fin))
+    res["parity"]["final_states_max_abs_diff_over_max"] = float(((m_fin - r_fin.view_as(m_fin)).abs().max() / r_fin.abs().max()).item())
+    del r_st, m_st
+    # chunk bmm and chunk scan
+    ms["ref_bmm_chunk"] = med(lambda: r_bmm._bmm_chunk_fwd(C, B, L, output_dtype=torch.float32))
+    ms["b200_bmm_chunk"] = med(lambda: bmm(C, B, L, output_dtype=torch.float32))
+    r_cb = r_bmm._bmm_chunk_fwd(C, B, L, output_dtype=torch.float32)
+    res["parity"]["cb_bit_equal_fraction"] = same(bmm(C, B, L, output_dtype=torch.float32), r_cb)
+    passed = r_out.view_as(m_out)
+    ms["ref_chunk_scan"] = med(lambda: r_scan._chunk_scan_fwd(r_cb, x, r_dt, r_dA, C, passed, D=D))
+    ms["b200_chunk_scan"] = med(lambda: scan(r_cb, x, r_dt, r_dA, C, passed, D=D))
+    r_y, _ = r_scan._chunk_scan_fwd(r_cb, x, r_dt, r_dA, C, passed, D=D)
+    m_y, _ = scan(r_cb, x, r_dt, r_dA, C, passed, D=D)
+    res["parity"]["out_bit_equal_fraction"] = same(m_y, r_y)
+    res["parity"]["out_max_abs_diff_over_max"] = float(((m_y.float() - r_y.float()).abs().max() / r_y.float().abs().max()).item())
+    ms["ref_state_path_unfused_total"] = ms["ref_chunk_cumsum"] + ms["ref_chunk_state"] + ms["ref_state_passing"]
+    ms["ref_forward_unfused_total"] = ms["ref_state_path_unfused_total"] + ms["ref_bmm_chunk"] + ms["ref_chunk_scan"]
+    ms["b200_forward_total"] = ms["b200_state_path_one_call"] + ms["b200_bmm_chunk"] + ms["b200_chunk_scan"]
+    res["recorded_earlier"] = {"ref_fused_concurrent_ms": 2.61, "ref_fused_globalbar_ms": 1.89,
+                               "note": "the reference's two fused kernels spin without a limit and are not re-run here; "
+                                       "these are the figures of a single earlier run on a B200 of this pool"}
+    return res
+
+
 SEQ1M = dict(name="seq-1m", batch=1, seqlen=1048576, nheads=80, headdim=64, ngroups=1, dstate=128, chunk_size=256)
 
 
@@ -416,6 +511,58 @@ def run_extras(args, rank, world, local, dist, dev):
     return extra
 
 
+def run_forward(args, rank, world, local):
+    """`--workload forward`: the reference's whole forward pipeline at the headline shape
+    (main.py:93-103 there: chunk bmm, state path, chunk scan), one GPU, per-kernel CUDA events.
+    Not the contract's metric: the line for profiling the two chunk GEMM kernels."""
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
+    from mamba_fused_minimal_b200.kernels.ssd_bmm import _bmm_chunk_fwd as bmm
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _chunk_scan_fwd as scan
+    from mamba_fused_minimal_b200.kernels.state_path import _state_path_fwd as state_path
+    w = dict(WORKLOAD)
+    if args.batch is not None:
+        w["batch"] = args.batch
+        w["name"] = f"{WORKLOAD['name']}-batch{args.batch}"
+    L = w["chunk_size"]
+    d = generate_benchmark_data(w["batch"], w["seqlen"], w["nheads"], w["headdim"], w["ngroups"], w["dstate"],
+                                dtype=torch.bfloat16, device=dev, seed=rank)
+    x, B, C, dt, A, bias, D = d["x"], d["B"], d["C"], d["dt"], d["A"], d["dt_bias"], d["D"].to(torch.bfloat16)
+
+    def step(ev=None):
+        if ev:
+            ev[0].record()
+        cb = bmm(C, B, L, output_dtype=torch.float32)
+        if ev:
+            ev[1].record()
+        dA, dto, passed, fin = state_path(dt, A, B, x, L, torch.bfloat16, dt_bias=bias, dt_softplus=True)
+        if ev:
+            ev[2].record()
+        y, _ = scan(cb, x, dto, dA, C, passed, D=D)
+        if ev:
+            ev[3].record()
+        return y, fin
+
+    ms = _timed_steps(step, args.steps, args.warmup, None, dev)
+    Kp = max(3, min(args.steps, 20))
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(Kp)]
+    for e in evs:
+        step(e)
+    torch.cuda.synchronize()
+    names = ["bmm_chunk_ms", "state_path_ms", "chunk_scan_ms"]
+    kernels = {n: statistics.median(e[i].elapsed_time(e[i + 1]) for e in evs) for i, n in enumerate(names)}
+    from mamba_fused_minimal_b200._ext import C as _C
+    _C.check_status(x)
+    if rank == 0:
+        print(json.dumps({"metric": "ssd_forward_tokens_per_s", "value": w["batch"] * w["seqlen"] / (ms * 1e-3),
+                          "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                          "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                          "config": dict(workload=w["name"] + " forward (bmm, state path, chunk scan)",
+                                         **{k: v for k, v in w.items() if k != "name"}),
+                          "kernels": kernels, "gpu_launches": 3 * args.steps}), flush=True)
+
+
 def run_seq1m(args, rank, world, local):
     """`--workload seq1m`: the long-context case as the line's own workload."""
     torch.cuda.set_device(local)
@@ -459,13 +606,17 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="profiling aid: device-resident timing only")
     ap.add_argument("--batch", type=int, default=None,
                     help="profiling aid: override the workload's batch (the bench line then names it)")
-    ap.add_argument("--workload", default="mamba2-2.7b-layer", choices=["mamba2-2.7b-layer", "seq1m"],
-                    help="seq1m: the 1 M-token sequence-parallel case (extra; the default is the contract's workload)")
+    ap.add_argument("--workload", default="mamba2-2.7b-layer", choices=["mamba2-2.7b-layer", "seq1m", "forward"],
+                    help="seq1m: the 1 M-token sequence-parallel case; forward: bmm + state path + chunk scan with "
+                         "per-kernel times (both extra; the default is the contract's workload)")
     ap.add_argument("--seqlen", type=int, default=None, help="seq1m only: override the sequence length")
     ap.add_argument("--summarise-ncu", default=None, metavar="CSV",
                     help="no benchmark: read `ncu -i REPORT --page raw --csv` output of a capture of this script and "
                          "write profiles/fused_state_kernel_traffic.json (use with --batch as captured)")
     ap.add_argument("--ncu-command", default="", help="with --summarise-ncu: the capture command, kept in the summary")
+    ap.add_argument("--reference-tree", default=None, metavar="PATH",
+                    help="a checkout of the reference project: also time ITS unfused Triton kernels on this GPU "
+                         "(key \"triton_unfused\"; single GPU only)")
     ap.add_argument("--no-extras", action="store_true", help="skip the extra multi-GPU cases (key \"extra\")")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -489,6 +640,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     if args.workload == "seq1m":
         run_seq1m(args, rank, world, local)
+        return
+    if args.workload == "forward":
+        run_forward(args, rank, world, local)
         return
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -672,6 +826,8 @@ def main():
         }
         if extra is not None:
             line["extra"] = extra
+        if args.reference_tree is not None and world == 1:
+            line["triton_unfused"] = reference_triton_unfused(args.reference_tree, w, dev)
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
             tok_s, t, n = cpu_hot_path(WORKLOAD["batch"], threads, 20)
