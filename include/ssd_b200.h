@@ -327,6 +327,29 @@ typedef struct {
 SSD_API int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * 6a. chunk bmm + chunk scan in one kernel.  Replaces the pair _bmm_chunk_fwd(C, B, ...) then
+ *    _chunk_scan_fwd(cb, ...) of the reference's pipelines (main.py:71-73 and :95,101;
+ *    kernels/ssd_bmm.py:64-72, kernels/ssd_chunk_scan.py:96-143): the chunk-local
+ *    cb[m, k] = C[m] . B[k] is computed on chip, tile by tile, by the kernel that consumes it, and
+ *    never exists in memory.  `scan` is read as for ssd_chunk_scan_fwd except that scan.cb, its
+ *    dtype and strides are ignored; B is (b, l, g, n) of scan.in_dtype.
+ *
+ *    Only the tcgen05 kernel implements this: 16-bit inputs, headdim 64, dstate 128, chunk size
+ *    128 or 256, no seq_idx, 16-byte aligned tensors with contiguous innermost dimensions.  For
+ *    anything else the call returns SSD_ERR_UNSUPPORTED and enqueues nothing; the caller then makes
+ *    the two separate calls (5) and (6).  Results agree with the two calls within the output
+ *    type's rounding (below the diagonal the decay factor is applied as two multiplications, see
+ *    the kernel; the rounding point before the dot product is the same).
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  ssd_chunk_scan_params_t scan;
+  const void* B;             /* (b, l, g, n) of scan.in_dtype */
+  int64_t B_stride[4];       /* b, l, g, n */
+} ssd_chunk_scan_fused_params_t;
+
+SSD_API int ssd_chunk_scan_fused_fwd(const ssd_chunk_scan_fused_params_t* prm, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * 7. sequence-parallel fix-up.  No counterpart in the reference (it is single-GPU,
  *    kernels/fused_concurrent.py:289); the carry it builds on is the reference's
  *    initial_states / final_states pair (kernels/ssd_state_passing.py:61-65,81).

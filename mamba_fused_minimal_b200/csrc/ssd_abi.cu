@@ -330,4 +330,21 @@ int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t stream) 
   return launch_chunk_scan_general(p, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int ssd_chunk_scan_fused_fwd(const ssd_chunk_scan_fused_params_t* prm, ssd_stream_t stream) {
+  SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
+  const ssd_chunk_scan_params_t& p = prm->scan;
+  SSD_REQUIRE(prm->B && p.x && p.dt && p.dA_cumsum && p.C && p.states && p.out, SSD_ERR_BAD_ARGUMENT,
+              "B, x, dt, dA_cumsum, C, states and out must not be NULL");
+  SSD_REQUIRE(p.z == nullptr || p.out_x != nullptr, SSD_ERR_BAD_ARGUMENT, "out_x is required when z is given");
+  SSD_REQUIRE(valid_dtype(p.in_dtype) && valid_dtype(p.states_dtype) && (p.D == nullptr || valid_dtype(p.D_dtype)),
+              SSD_ERR_BAD_ARGUMENT, "bad dtype");
+  SSD_REQUIRE(p.batch > 0 && p.seqlen > 0 && p.nheads > 0 && p.headdim > 0 && p.ngroups > 0 && p.dstate > 0 &&
+                  p.chunk_size > 0 && p.nheads % p.ngroups == 0,
+              SSD_ERR_BAD_ARGUMENT, "bad sizes");
+  SSD_REQUIRE(scan_fused_ok(*prm), SSD_ERR_UNSUPPORTED,
+              "the fused chunk bmm + chunk scan kernel does not take this problem: call ssd_bmm_chunk_fwd and "
+              "ssd_chunk_scan_fwd");
+  return launch_chunk_scan_fused(*prm, reinterpret_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -484,6 +484,374 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
   }
 }
 
+// =====================================================================================
+// chunk scan with the chunk-local C . B^T computed on chip (the reference's _bmm_chunk_fwd and
+// _chunk_scan_fwd, kernels/ssd_bmm.py:64-72 and kernels/ssd_chunk_scan.py:96-143, in one kernel)
+// =====================================================================================
+// Same tile (128 positions m of one (batch, chunk, head) x 64 headdim columns), same two
+// accumulators and the same rounding point as chunk_scan_kernel.  What differs:
+//   * cb[m, k] is not read from memory.  Per unit of 64 positions k the MMA thread multiplies the
+//     staged C tile (the A operand of acc1) by the unit's B tile (64 x 128, TMA, K-major) into a
+//     128 x 64 fp32 block in tensor memory -- the MMA the stand-alone bmm kernel issues, so the
+//     values are the same -- and a row thread fetches its 32 values with one tcgen05.ld.  The
+//     (b, c, g, L, L) tensor, its TMA ring and its shared-memory reads are gone.  The block is free
+//     again as soon as the row threads hold it in registers, so the next unit's product is ready
+//     long before it is needed.
+//   * Units are 64 positions wide (four per 256-position chunk): half as many hand-offs between the
+//     row threads and the MMA thread as with 32.
+//   * Below the diagonal the decay is applied in factors: exp(a_m - a_k) dt_k =
+//     exp(a_m - a_e) * [exp(a_e - a_k) dt_k] with e the unit's last position.  The bracket is one
+//     vector per chunk (built once per CTA), the first factor one exp per row and unit: two
+//     multiplications per (m, k) pair instead of an exp and four operations.  Both exponents are <= 0
+//     there (a is non-increasing), so nothing overflows.  In the unit that holds the diagonal, and in
+//     a chunk whose cumulative sums are not non-increasing (positive A), every pair is evaluated as
+//     exp(min(a_m - a_k, 0)) dt_k exactly like the other kernel.
+//   * TMA and MMA issue are two threads in two warps: neither waits for the other's barriers.
+constexpr int kFsU = 64;               // positions per unit
+constexpr int kFsBSlots = 2;           // ring of B tiles (released by the cb MMAs)
+constexpr int kFsXSlots = 3;           // ring of x tiles (released by the acc2 MMAs)
+constexpr int kFsThreads = (kScanRowWarps + 2) * 32;
+enum FusedScanWait { kFsWaitCbFull = 311, kFsWaitCbFree, kFsWaitBFull, kFsWaitBFree, kFsWaitXFull, kFsWaitXFree };
+
+template <typename T>
+__global__ void __launch_bounds__(kFsThreads, 2)
+chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_constant__ CUtensorMap tmap_S,
+                        const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_B,
+                        const ScanArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int L = a.L;
+  constexpr uint32_t kCBox = kScanRows * 128, kSBox = kScanP * 128;          // one 64-n box of C / of the state
+  constexpr uint32_t kBBox = kFsU * 128;                                      // one 64-n box of a unit's B rows
+  constexpr uint32_t kBTile = 2 * kBBox, kXTile = kFsU * 128;                 // 16 KiB, 8 KiB
+  constexpr uint32_t kOffS = 2 * kCBox, kOffB = kOffS + 2 * kSBox, kOffX = kOffB + kFsBSlots * kBTile;
+  constexpr uint32_t kOffVec = kOffX + kFsXSlots * kXTile;
+  constexpr uint32_t kOffCtl = kOffVec + 3 * 256 * 4;
+  float* dA_s = reinterpret_cast<float*>(smem + kOffVec);
+  float* dt_s = dA_s + 256;
+  float* cv_s = dt_s + 256;                      // exp(a_e - a_k) * dt_k, e = last position of k's unit
+  const uint32_t bars = sbase + kOffCtl;
+  const uint32_t bar_cs = bars, bar_acc = bars + 8, bar_cb_full = bars + 16, bar_cb_free = bars + 24;
+  auto bar_b_full = [&](int i) { return bars + 32 + 8u * i; };
+  auto bar_b_free = [&](int i) { return bars + 48 + 8u * i; };
+  auto bar_x_full = [&](int i) { return bars + 64 + 8u * i; };
+  auto bar_x_free = [&](int i) { return bars + 88 + 8u * i; };
+  auto bar_a_ready = [&](int i) { return bars + 112 + 8u * i; };
+  volatile int* ctl = reinterpret_cast<volatile int*>(smem + kOffCtl + 128);    // [0] abort, [1] tmem
+  WaitCtx wc{ctl, a.status, a.wait_limit};
+
+  const int mt = blockIdx.x;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z / a.nchunks, c = blockIdx.z % a.nchunks;
+  const int g = h / (a.nheads / a.ngroups);
+  const int limit = min(L, a.seqlen - c * L);
+  const int nu = min((kScanRows / kFsU) * (mt + 1), (limit + kFsU - 1) / kFsU);
+  constexpr int kMmaWarp = kScanRowWarps, kTmaWarp = kScanRowWarps + 1;
+
+  auto load_B = [&](int u) {                        // TMA thread only
+    const int s = u % kFsBSlots;
+    const uint32_t dst = sbase + kOffB + s * kBTile;
+    mbar_expect_tx(bar_b_full(s), kBTile);
+    tma_load_4d(dst, &tmap_B, bar_b_full(s), 0, g, c * L + u * kFsU, b);
+    tma_load_4d(dst + kBBox, &tmap_B, bar_b_full(s), 64, g, c * L + u * kFsU, b);
+  };
+  auto load_x = [&](int u) {
+    const int s = u % kFsXSlots;
+    mbar_expect_tx(bar_x_full(s), kXTile);
+    tma_load_4d(sbase + kOffX + s * kXTile, &tmap_x, bar_x_full(s), 0, h, c * L + u * kFsU, b);
+  };
+  if (warp == kTmaWarp && lane == 0) {
+    mbar_init(bar_cs, 1);
+    mbar_init(bar_acc, 1);
+    mbar_init(bar_cb_full, 1);
+    mbar_init(bar_cb_free, kScanRowWarps);
+    for (int i = 0; i < kFsBSlots; ++i) { mbar_init(bar_b_full(i), 1); mbar_init(bar_b_free(i), 1); }
+    for (int i = 0; i < kFsXSlots; ++i) { mbar_init(bar_x_full(i), 1); mbar_init(bar_x_free(i), 1); }
+    for (int i = 0; i < 2; ++i) mbar_init(bar_a_ready(i), kScanRowWarps);
+    ctl[0] = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    // the first loads are on their way while the rest of the CTA sets up
+    mbar_expect_tx(bar_cs, 2 * kCBox + 2 * kSBox);
+    for (int kb = 0; kb < 2; ++kb) {
+      tma_load_4d(sbase + kb * kCBox, &tmap_C, bar_cs, kb * 64, g, c * L + mt * kScanRows, b);
+      tma_load_5d(sbase + kOffS + kb * kSBox, &tmap_S, bar_cs, kb * 64, 0, h, c, b);
+    }
+    for (int u = 0; u < nu && u < kFsBSlots; ++u) load_B(u);
+    for (int u = 0; u < nu && u < kFsXSlots; ++u) load_x(u);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(sbase + kOffCtl + 132, 256);
+    tmem_relinquish();
+  } else if (warp < kScanRowWarps) {
+    const float* dAr = a.dA + (int64_t)b * a.dA_s[0] + (int64_t)h * a.dA_s[1] + (int64_t)c * a.dA_s[2];
+    const float* dtr = a.dt + (int64_t)b * a.dt_s[0] + (int64_t)h * a.dt_s[1] + (int64_t)c * a.dt_s[2];
+    for (int k = tid; k < L; k += kScanRowWarps * 32) {
+      dA_s[k] = dAr[k];
+      dt_s[k] = dtr[k];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // per-position factor of the factored form, and whether this chunk allows it
+  int bad = 0;
+  if (warp < kScanRowWarps) {
+    for (int k = tid; k < L; k += kScanRowWarps * 32) {
+      const float ak = dA_s[k];
+      cv_s[k] = fast_exp(dA_s[k | (kFsU - 1)] - ak) * dt_s[k];
+      if (k > 0 && !(ak <= dA_s[k - 1])) bad = 1;
+    }
+  }
+  const bool exact_only = __syncthreads_or(bad) != 0;
+  const uint32_t tmem_base = static_cast<uint32_t>(ctl[1]);
+  constexpr uint32_t kAcc1 = 0, kAcc2 = 64, kCB = 128, kA2 = 192;     // TMEM columns: one cb block of 64, two A2 slots of 32
+
+  if (warp == kTmaWarp) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int u = 0; u < nu && ok; ++u) {
+        if (u + kFsBSlots < nu) {
+          ok = mbar_wait(bar_b_free(u % kFsBSlots), (u / kFsBSlots) & 1, wc, kFsWaitBFree);
+          if (!ok) break;
+          load_B(u + kFsBSlots);
+        }
+        if (u + kFsXSlots < nu) {
+          ok = mbar_wait(bar_x_free(u % kFsXSlots), (u / kFsXSlots) & 1, wc, kFsWaitXFree);
+          if (!ok) break;
+          load_x(u + kFsXSlots);
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      bool ok = mbar_wait(bar_cs, 0, wc, kScanWaitCS);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t idesc1 = mma_idesc(Pack16<T>::kFmt, false, false, kScanRows, kScanP);
+        for (int k16 = 0; k16 < kScanN / 16; ++k16) {
+          const uint32_t koff = (k16 & 3) * 32;
+          const uint64_t ad = smem_desc_sw128(sbase + (k16 >> 2) * kCBox + koff, 16, 1024);
+          const uint64_t bd = smem_desc_sw128(sbase + kOffS + (k16 >> 2) * kSBox + koff, 16, 1024);
+          mma_f16_ss(tmem_base + kAcc1, ad, bd, idesc1, k16 != 0 ? 1u : 0u);
+        }
+        const uint32_t idesc_cb = mma_idesc(Pack16<T>::kFmt, false, false, kScanRows, kFsU);
+        const uint32_t idesc2 = mma_idesc(Pack16<T>::kFmt, false, true, kScanRows, kScanP);
+        for (int u = 0; u <= nu && ok; ++u) {
+          if (u < nu) {
+            // cb block of unit u: C tile (128 x 128, K-major) . B unit tile (64 x 128, K-major)^T
+            const int s = u % kFsBSlots;
+            ok = mbar_wait(bar_b_full(s), (u / kFsBSlots) & 1, wc, kFsWaitBFull);
+            if (!ok) break;
+            if (u > 0) {                               // the row threads hold unit u - 1's block in registers
+              ok = mbar_wait(bar_cb_free, (u - 1) & 1, wc, kFsWaitCbFree);
+              if (!ok) break;
+            }
+            tc_fence_after();
+            for (int k16 = 0; k16 < kScanN / 16; ++k16) {
+              const uint32_t koff = (k16 & 3) * 32;
+              const uint64_t ad = smem_desc_sw128(sbase + (k16 >> 2) * kCBox + koff, 16, 1024);
+              const uint64_t bd = smem_desc_sw128(sbase + kOffB + s * kBTile + (k16 >> 2) * kBBox + koff, 16, 1024);
+              mma_f16_ss(tmem_base + kCB, ad, bd, idesc_cb, k16 != 0 ? 1u : 0u);
+            }
+            mma_commit(bar_cb_full);
+            mma_commit(bar_b_free(s));
+          }
+          if (u > 0) {
+            // acc2 += A2(u - 1) . x(u - 1): A2 from tensor memory (K-major by construction), x MN-major as loaded
+            const int v = u - 1, sx = v % kFsXSlots;
+            ok = mbar_wait(bar_x_full(sx), (v / kFsXSlots) & 1, wc, kFsWaitXFull);
+            if (!ok) break;
+            ok = mbar_wait(bar_a_ready(v & 1), (v >> 1) & 1, wc, kScanWaitAReady);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t bd0 = smem_desc_sw128(sbase + kOffX + sx * kXTile, kXTile, 1024);
+            for (int k16 = 0; k16 < kFsU / 16; ++k16)
+              mma_f16_ts(tmem_base + kAcc2, tmem_base + kA2 + (v & 1) * (kFsU / 2) + k16 * 8,
+                         bd0 + (uint64_t)((k16 * 2048) >> 4), idesc2, (v | k16) != 0 ? 1u : 0u);
+            mma_commit(bar_x_free(sx));
+          }
+        }
+        if (ok) mma_commit(bar_acc);
+      }
+    }
+  } else {
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;                    // row of the tile = TMEM lane
+    const int half = warp >> 2;                      // which 32 positions of a unit / which 32 headdim columns
+    const int m = mt * kScanRows + r;                // position inside the chunk
+    const float am = dA_s[min(m, L - 1)];
+    const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+    const int udiag = (mt * kScanRows + wq * 32) / kFsU;   // the unit that holds this warp's rows
+    bool ok = true;
+    for (int u = 0; u < nu && ok; ++u) {
+      const int k0 = u * kFsU + half * 32;
+      ok = mbar_wait(bar_cb_full, u & 1, wc, kFsWaitCbFull);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t o[16];
+      float v[32];
+      const bool above = u > udiag;                  // wholly above the diagonal
+      if (!above) {
+        uint32_t raw[32];
+        tmem_ld_32x32(tmem_base + lane_sel + kCB + half * 32, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_cb_free);       // the block may take the next unit
+      if (above) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = 0u;
+      } else {
+        if (u == udiag || exact_only) {
+          // cb * exp(min(a_m - a_k, 0)) * dt_k, two positions per instruction
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(dA_s + k0 + i);
+            const float4 d = *reinterpret_cast<const float4*>(dt_s + k0 + i);
+            const float ak[4] = {t.x, t.y, t.z, t.w}, dk[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+            for (int jj = 0; jj < 4; jj += 2) {
+              float2 dl = __ffma2_rn(make_float2(ak[jj], ak[jj + 1]), make_float2(-1.0f, -1.0f), make_float2(am, am));
+              dl.x = fminf(dl.x, 0.0f);
+              dl.y = fminf(dl.y, 0.0f);
+              dl = __fmul2_rn(dl, make_float2(1.4426950408889634f, 1.4426950408889634f));
+              const float2 e = make_float2(ex2_approx(dl.x), ex2_approx(dl.y));
+              float2 w = __fmul2_rn(make_float2(v[i + jj], v[i + jj + 1]), e);
+              w = __fmul2_rn(w, make_float2(dk[jj], dk[jj + 1]));
+              v[i + jj] = w.x;
+              v[i + jj + 1] = w.y;
+            }
+          }
+          if (u == udiag) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (k0 + i > m) v[i] = 0.0f;
+          }
+        } else {
+          // (cb * exp(a_m - a_e)) * [exp(a_e - a_k) * dt_k]
+          const float rm = fast_exp(am - dA_s[u * kFsU + kFsU - 1]);
+          const float2 rm2 = make_float2(rm, rm);
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 cvv = *reinterpret_cast<const float4*>(cv_s + k0 + i);
+            float2 w0 = __fmul2_rn(make_float2(v[i], v[i + 1]), rm2);
+            float2 w1 = __fmul2_rn(make_float2(v[i + 2], v[i + 3]), rm2);
+            w0 = __fmul2_rn(w0, make_float2(cvv.x, cvv.y));
+            w1 = __fmul2_rn(w1, make_float2(cvv.z, cvv.w));
+            v[i] = w0.x; v[i + 1] = w0.y; v[i + 2] = w1.x; v[i + 3] = w1.y;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = PackPair<T>::pack(v[2 * i], v[2 * i + 1]);
+      }
+      // the A2 slot is free once the MMAs of unit u - 2 are complete, which is what frees that unit's x tile
+      if (u >= 2) {
+        ok = mbar_wait(bar_x_free((u - 2) % kFsXSlots), ((u - 2) / kFsXSlots) & 1, wc, kFsWaitXFree);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      tmem_st_32x32b_x16(tmem_base + lane_sel + kA2 + (u & 1) * (kFsU / 2) + half * 16, o);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_a_ready(u & 1));
+    }
+    // ---- epilogue: out = exp(a_m) * acc1 + acc2 + D * x[m]
+    const bool live = m < limit;
+    const int q = half;
+    const int64_t pos = (int64_t)c * L + m;
+    const uint8_t* xrow = static_cast<const uint8_t*>(a.x) +
+                          2 * ((int64_t)b * a.x_s[0] + pos * a.x_s[1] + (int64_t)h * a.x_s[2]) + q * 64;
+    uint4 xr[4];
+    if (a.D != nullptr && live) {                    // requested before the wait, used after it
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) xr[pc] = __ldg(reinterpret_cast<const uint4*>(xrow) + pc);
+    }
+    uint4 zr[4];
+    if (a.z != nullptr && live) {
+      const uint8_t* zrow = static_cast<const uint8_t*>(a.z) +
+                            2 * ((int64_t)b * a.z_s[0] + pos * a.z_s[1] + (int64_t)h * a.z_s[2]) + q * 64;
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) zr[pc] = __ldg(reinterpret_cast<const uint4*>(zrow) + pc);
+    }
+    const float dh = (a.D != nullptr && !a.D_has_hdim) ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride) : 0.0f;
+    if (ok) ok = mbar_wait(bar_acc, 0, wc, kScanWaitAcc, 64);
+    if (ok) {
+      tc_fence_after();
+      const float sm = fast_exp(am);
+      uint8_t* orow = static_cast<uint8_t*>(a.out) +
+                      2 * ((int64_t)b * a.out_s[0] + pos * a.out_s[1] + (int64_t)h * a.out_s[2]) + q * 64;
+      uint32_t r1[32], r2[32];
+      tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
+      tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
+      tmem_ld_wait();
+      float res[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) res[i] = __uint_as_float(r1[i]) * sm + __uint_as_float(r2[i]);
+      if (a.D != nullptr && live) {
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {             // 16-byte pieces = 8 headdim columns
+          const uint32_t w[4] = {xr[pc].x, xr[pc].y, xr[pc].z, xr[pc].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float x0, x1;
+            PackPair<T>::unpack(w[i], x0, x1);
+            const int pcol = q * 32 + pc * 8 + 2 * i;
+            const float d0 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol) : dh;
+            const float d1 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol + 1) : dh;
+            res[pc * 8 + 2 * i] += x0 * d0;
+            res[pc * 8 + 2 * i + 1] += x1 * d1;
+          }
+        }
+      }
+      if (a.z != nullptr && live) {
+        uint8_t* oxrow = static_cast<uint8_t*>(a.out_x) +
+                         2 * ((int64_t)b * a.out_s[0] + pos * a.out_s[1] + (int64_t)h * a.out_s[2]) + q * 64;
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 t;
+          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
+          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
+          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
+          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
+          *reinterpret_cast<uint4*>(oxrow + pc * 16) = t;
+          const uint32_t w[4] = {zr[pc].x, zr[pc].y, zr[pc].z, zr[pc].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float z0, z1;
+            PackPair<T>::unpack(w[i], z0, z1);
+            res[pc * 8 + 2 * i] *= z0 * (1.0f / (1.0f + expf(-z0)));
+            res[pc * 8 + 2 * i + 1] *= z1 * (1.0f / (1.0f + expf(-z1)));
+          }
+        }
+      }
+      if (live) {
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 t;
+          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
+          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
+          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
+          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
+          *reinterpret_cast<uint4*>(orow + pc * 16) = t;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
 }  // namespace
 
 int gemm_wait_status(int* code) {
@@ -619,6 +987,71 @@ int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
   kern<<<grid, kScanThreads, smem, stream>>>(mC, mS, mx, mcb, a);
+  SSD_CUDA_OK(cudaGetLastError());
+  return SSD_OK;
+}
+
+// 1 if the on-chip-cb chunk-scan kernel takes this problem: what scan_fast_ok asks of everything but
+// cb, and B laid out like C.
+int scan_fused_ok(const ssd_chunk_scan_fused_params_t& f) {
+  ssd_chunk_scan_params_t p = f.scan;
+  // (stand-ins so that the shared checks pass for the tensor this kernel does not read)
+  p.cb = p.C;
+  p.cb_dtype = SSD_F32;
+  for (int i = 0; i < 4; ++i) p.cb_stride[i] = 4;
+  p.cb_stride[4] = 1;
+  if (!scan_fast_ok(p)) return 0;
+  if (f.B == nullptr || f.B_stride[3] != 1 || (reinterpret_cast<uintptr_t>(f.B) & 15)) return 0;
+  for (int i = 0; i < 3; ++i)
+    if (f.B_stride[i] % 8 != 0) return 0;
+  return 1;
+}
+
+int launch_chunk_scan_fused(const ssd_chunk_scan_fused_params_t& f, cudaStream_t stream) {
+  const ssd_chunk_scan_params_t& p = f.scan;
+  const int L = p.chunk_size;
+  const int nchunks = (p.seqlen + L - 1) / L;
+  SSD_REQUIRE((long long)p.batch * nchunks <= 65535, SSD_ERR_UNSUPPORTED, "chunk scan grid too large");
+  CUtensorMap mC, mS, mx, mB;
+  int rc = make_rows_map(&mC, p.C, p.in_dtype, p.dstate, p.ngroups, p.seqlen, p.batch, p.C_stride, kScanRows);
+  if (rc != SSD_OK) return rc;
+  rc = make_rows_map(&mx, p.x, p.in_dtype, p.headdim, p.nheads, p.seqlen, p.batch, p.x_stride, kFsU);
+  if (rc != SSD_OK) return rc;
+  rc = make_rows_map(&mB, f.B, p.in_dtype, p.dstate, p.ngroups, p.seqlen, p.batch, f.B_stride, kFsU);
+  if (rc != SSD_OK) return rc;
+  rc = make_states_map(&mS, p.states, p.in_dtype, p.nheads, nchunks, p.batch, p.states_stride);
+  if (rc != SSD_OK) return rc;
+  ScanArgs a{};
+  a.x = p.x;
+  a.z = p.z;
+  a.out_x = p.out_x;
+  a.dt = p.dt;
+  a.dA = p.dA_cumsum;
+  a.D = p.D;
+  a.out = p.out;
+  SSD_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&a.status), g_scan_status));
+  for (int i = 0; i < 3; ++i) {
+    a.dt_s[i] = p.dt_stride[i];
+    a.dA_s[i] = p.dA_stride[i];
+    a.out_s[i] = p.out_stride[i];
+    a.x_s[i] = p.x_stride[i];
+    a.z_s[i] = p.z_stride[i];
+  }
+  a.D_stride = p.D_stride;
+  a.D_dtype = p.D_dtype;
+  a.D_has_hdim = p.D_has_hdim;
+  a.L = L;
+  a.seqlen = p.seqlen;
+  a.nheads = p.nheads;
+  a.ngroups = p.ngroups;
+  a.nchunks = nchunks;
+  a.wait_limit = wait_limit_cycles();
+  const int smem = 2 * kScanRows * 128 + 2 * kScanP * 128 + kFsBSlots * 2 * kFsU * 128 + kFsXSlots * kFsU * 128 +
+                   3 * 256 * 4 + 256 + 1024;
+  auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_fused_kernel<__nv_bfloat16> : chunk_scan_fused_kernel<__half>;
+  SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
+  kern<<<grid, kFsThreads, smem, stream>>>(mC, mS, mx, mB, a);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }

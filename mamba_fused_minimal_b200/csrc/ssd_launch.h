@@ -71,5 +71,8 @@ int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream);
 int gemm_wait_status(int* code);
 int scan_fast_ok(const ssd_chunk_scan_params_t& p);
 int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream);
+// The chunk scan that computes the chunk-local C . B^T itself (no cb tensor).
+int scan_fused_ok(const ssd_chunk_scan_fused_params_t& f);
+int launch_chunk_scan_fused(const ssd_chunk_scan_fused_params_t& f, cudaStream_t stream);
 
 }  // namespace ssd

@@ -620,6 +620,76 @@ std::tuple<Tensor, OptTensor> chunk_scan_fwd(const Tensor& cb, const Tensor& x, 
   return {out, out_x};
 }
 
+// Chunk bmm + chunk scan behind one call: (out, out_x) from C, B instead of a cb tensor.  One
+// kernel where the tcgen05 kernel takes the problem (cb never exists in memory); otherwise
+// ssd_bmm_chunk_fwd into a temporary and ssd_chunk_scan_fwd.
+std::tuple<Tensor, OptTensor> chunk_scan_combined_fwd(const Tensor& C, const Tensor& B, const Tensor& x, const Tensor& dt,
+                                                     const Tensor& dA_cumsum, const Tensor& states, const OptTensor& D,
+                                                     const OptTensor& z, const OptTensor& seq_idx) {
+  TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor (libssd_b200 has no CPU path)");
+  for (const Tensor* t : {&B, &dt, &dA_cumsum, &C, &states}) check_cuda(*t, x, "chunk_scan input");
+  TORCH_CHECK(C.scalar_type() == x.scalar_type() && B.scalar_type() == x.scalar_type(), "B, C and x must have the same dtype");
+  TORCH_CHECK(dt.scalar_type() == at::kFloat && dA_cumsum.scalar_type() == at::kFloat, "dt and dA_cumsum must be fp32");
+  TORCH_CHECK(x.dim() == 4 && B.dim() == 4 && C.dim() == 4 && dt.dim() == 4 && states.dim() == 5 && B.sizes() == C.sizes(),
+              "x (b, l, h, p), B and C (b, l, g, n), dt (b, h, c, L), states (b, c, h, p, n)");
+  const int64_t chunk_size = dt.size(3);
+  bool try_fused = !seq_idx.has_value();
+  if (try_fused) {
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor out = torch::empty({x.size(0), x.size(1), x.size(2), x.size(3)}, x.options());
+    OptTensor out_x;
+    ssd_chunk_scan_fused_params_t f{};
+    ssd_chunk_scan_params_t& p = f.scan;
+    p.x = x.data_ptr();
+    p.dt = dt.data_ptr<float>();
+    p.dA_cumsum = dA_cumsum.data_ptr<float>();
+    p.C = C.data_ptr();
+    p.states = states.data_ptr();
+    p.out = out.data_ptr();
+    p.cb_dtype = SSD_F32;
+    p.in_dtype = dtype_code(x, "x");
+    p.states_dtype = dtype_code(states, "states");
+    p.batch = x.size(0);
+    p.seqlen = x.size(1);
+    p.nheads = x.size(2);
+    p.headdim = x.size(3);
+    p.ngroups = C.size(2);
+    p.dstate = C.size(3);
+    p.chunk_size = chunk_size;
+    copy_strides(p.x_stride, x, {0, 1, 2, 3});
+    copy_strides(p.out_stride, out, {0, 1, 2, 3});
+    copy_strides(p.dt_stride, dt, {0, 1, 2, 3});
+    copy_strides(p.dA_stride, dA_cumsum, {0, 1, 2, 3});
+    copy_strides(p.C_stride, C, {0, 1, 2, 3});
+    copy_strides(p.states_stride, states, {0, 1, 2, 3, 4});
+    f.B = B.data_ptr();
+    copy_strides(f.B_stride, B, {0, 1, 2, 3});
+    Tensor Dh, zh;
+    if (D.has_value()) {
+      check_cuda(*D, x, "D");
+      Dh = D->dim() == 2 && D->stride(1) != 1 ? D->contiguous() : *D;
+      p.D = Dh.data_ptr();
+      p.D_dtype = dtype_code(Dh, "D");
+      p.D_has_hdim = Dh.dim() == 2 ? 1 : 0;
+      p.D_stride = Dh.stride(0);
+    }
+    if (z.has_value()) {
+      check_cuda(*z, x, "z");
+      TORCH_CHECK(z->scalar_type() == x.scalar_type(), "z and x must have the same dtype");
+      zh = *z;
+      p.z = zh.data_ptr();
+      copy_strides(p.z_stride, zh, {0, 1, 2, 3});
+      out_x = torch::empty_like(out);
+      p.out_x = out_x->data_ptr();
+    }
+    const int rc = ssd_chunk_scan_fused_fwd(&f, current_stream(x));
+    if (rc == SSD_OK) return {out, out_x};
+    TORCH_CHECK(rc == SSD_ERR_UNSUPPORTED, "ssd_chunk_scan_fused_fwd failed (status ", rc, "): ", ssd_last_error());
+  }
+  Tensor cb = bmm_chunk_fwd(C, B, chunk_size, seq_idx, false, at::kFloat);
+  return chunk_scan_fwd(cb, x, dt, dA_cumsum, C, states, D, z, seq_idx);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -654,6 +724,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("debug_set_flags", [](int64_t flags) { ssd_debug_set_flags((int)flags); });
   m.def("bmm_chunk_fwd", &bmm_chunk_fwd, py::arg("a"), py::arg("b"), py::arg("chunk_size"),
         py::arg("seq_idx") = py::none(), py::arg("causal") = false, py::arg("output_dtype") = py::none());
+  m.def("chunk_scan_combined_fwd", &chunk_scan_combined_fwd, py::arg("C"), py::arg("B"), py::arg("x"), py::arg("dt"),
+        py::arg("dA_cumsum"), py::arg("states"), py::arg("D") = py::none(), py::arg("z") = py::none(),
+        py::arg("seq_idx") = py::none());
   m.def("chunk_scan_fwd", &chunk_scan_fwd, py::arg("cb"), py::arg("x"), py::arg("dt"), py::arg("dA_cumsum"),
         py::arg("C"), py::arg("states"), py::arg("D") = py::none(), py::arg("z") = py::none(),
         py::arg("seq_idx") = py::none());

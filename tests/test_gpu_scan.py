@@ -63,3 +63,75 @@ def test_chunk_scan_fast_and_plain_kernels_agree(cuda_device):
     # identical rounding points; only the order of the fp32 additions differs
     assert ((out_f.float() - out_p.float()).abs().max() / scale).item() <= 1e-2
     assert (out_f == out_p).float().mean().item() > 0.99
+
+
+# ---- chunk bmm + chunk scan in one kernel (`_bmm_chunk_scan_fwd`) --------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,l,h,g,L,d_hdim,with_d", [(2, 1024, 4, 1, 256, False, True), (1, 700, 6, 2, 256, True, True),
+                                                      (2, 384, 2, 2, 128, False, False), (1, 130, 2, 1, 128, False, True)])
+def test_bmm_chunk_scan_one_kernel_against_oracle_and_two_calls(cuda_device, dtype, b, l, h, g, L, d_hdim, with_d):
+    """The kernel that computes C . B^T on chip against the oracle (atol = rtol = 1e-2 of the tensor's
+    max) and against `_bmm_chunk_fwd` + `_chunk_scan_fwd` (same rounding point; the decay below the
+    diagonal is applied as two multiplications, so the two agree to a bf16 step on rare elements)."""
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _bmm_chunk_scan_fwd, _chunk_scan_fwd
+    inp, d, dA, dt, passed, cb, D = _case(cuda_device, dtype, b, l, h, g, L, seed=l + h, d_hdim=d_hdim, with_d=with_d)
+    Dd = None if D is None else D.to(cuda_device)
+    out, _ = _bmm_chunk_scan_fwd(d["C"], d["B"], d["x"], dt, dA, passed, D=Dd)
+    two, _ = _chunk_scan_fwd(cb, d["x"], dt, dA, d["C"], passed, D=Dd)
+    ref, _ = O.chunk_scan_fwd(cb.cpu(), inp["x"], dt.cpu(), dA.cpu(), inp["C"], passed.cpu(), D=D, exp_impl="ex2")
+    scale = ref.float().abs().max()
+    torch.testing.assert_close(out.float().cpu() / scale, ref.float() / scale, atol=1e-2, rtol=1e-2)
+    assert torch.isfinite(out).all()
+    diff = (out.float() - two.float()).abs().max().item() / scale.item()
+    assert diff <= 2.0 ** -7, diff
+    assert (out == two).float().mean().item() > 0.99
+    from mamba_fused_minimal_b200._ext import C
+    C.check_status(d["x"])
+
+
+def test_bmm_chunk_scan_one_kernel_gate_and_fast_decay(cuda_device):
+    """z gating through the one-kernel route, and decays so fast that the factors underflow
+    (nothing may turn into NaN or infinity: both exponents of the factored form are <= 0)."""
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _bmm_chunk_scan_fwd
+    dtype = torch.bfloat16
+    inp, d, dA, dt, passed, cb, D = _case(cuda_device, dtype, 2, 700, 4, 2, 256, seed=11)
+    z = torch.randn(2, 700, 4, 64, generator=torch.Generator().manual_seed(12)).to(dtype)
+    out, out_x = _bmm_chunk_scan_fwd(d["C"], d["B"], d["x"], dt, dA, passed, D=D.to(cuda_device), z=z.to(cuda_device))
+    ref, ref_x = O.chunk_scan_fwd(cb.cpu(), inp["x"], dt.cpu(), dA.cpu(), inp["C"], passed.cpu(), D=D, z=z, exp_impl="ex2")
+    for got, want in ((out, ref), (out_x, ref_x)):
+        scale = want.float().abs().max()
+        torch.testing.assert_close(got.float().cpu() / scale, want.float() / scale, atol=1e-2, rtol=1e-2)
+    # very fast decay: A = -200, dt up to 4 -> per-position exponents of several hundred
+    dA_fast = dA * 40.0
+    dt_big = dt * 10.0
+    out_f, _ = _bmm_chunk_scan_fwd(d["C"], d["B"], d["x"], dt_big, dA_fast, passed, D=D.to(cuda_device))
+    ref_f, _ = O.chunk_scan_fwd(cb.cpu(), inp["x"], dt_big.cpu(), dA_fast.cpu(), inp["C"], passed.cpu(), D=D, exp_impl="ex2")
+    assert torch.isfinite(out_f).all()
+    scale = ref_f.float().abs().max()
+    torch.testing.assert_close(out_f.float().cpu() / scale, ref_f.float() / scale, atol=1e-2, rtol=1e-2)
+
+
+def test_bmm_chunk_scan_one_kernel_increasing_cumsum(cuda_device):
+    """Positive A makes the cumulative sums increase; the clamp exp(min(a_m - a_k, 0)) then matters and
+    the kernel must take its exact path for every unit."""
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _bmm_chunk_scan_fwd
+    dtype = torch.bfloat16
+    inp, d, dA, dt, passed, cb, D = _case(cuda_device, dtype, 1, 512, 2, 1, 256, seed=5)
+    dA_pos = -dA * 0.05
+    out, _ = _bmm_chunk_scan_fwd(d["C"], d["B"], d["x"], dt, dA_pos, passed, D=D.to(cuda_device))
+    ref, _ = O.chunk_scan_fwd(cb.cpu(), inp["x"], dt.cpu(), dA_pos.cpu(), inp["C"], passed.cpu(), D=D, exp_impl="ex2")
+    scale = ref.float().abs().max()
+    torch.testing.assert_close(out.float().cpu() / scale, ref.float() / scale, atol=1e-2, rtol=1e-2)
+
+
+def test_bmm_chunk_scan_falls_back_to_two_kernels(cuda_device):
+    """fp32 inputs / seq_idx: no one-kernel route; the call makes the two separate calls itself."""
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _bmm_chunk_scan_fwd, _chunk_scan_fwd
+    inp, d, dA, dt, passed, cb, D = _case(cuda_device, torch.bfloat16, 1, 512, 4, 1, 128, seed=9)
+    si = torch.zeros(1, 512, dtype=torch.int32, device=cuda_device)
+    a, _ = _bmm_chunk_scan_fwd(d["C"], d["B"], d["x"], dt, dA, passed, D=D.to(cuda_device), seq_idx=si)
+    from mamba_fused_minimal_b200.kernels.ssd_bmm import _bmm_chunk_fwd
+    cb_si = _bmm_chunk_fwd(d["C"], d["B"], 128, seq_idx=si, output_dtype=torch.float32)
+    b2, _ = _chunk_scan_fwd(cb_si, d["x"], dt, dA, d["C"], passed, D=D.to(cuda_device), seq_idx=si)
+    assert torch.equal(a, b2)
