@@ -519,7 +519,7 @@ def run_forward(args, rank, world, local):
     dev = torch.device("cuda", local)
     from mamba_fused_minimal_b200.kernels.rand_data import generate_benchmark_data
     from mamba_fused_minimal_b200.kernels.ssd_bmm import _bmm_chunk_fwd as bmm
-    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _chunk_scan_fwd as scan
+    from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _bmm_chunk_scan_fwd as bmm_scan, _chunk_scan_fwd as scan
     from mamba_fused_minimal_b200.kernels.state_path import _state_path_fwd as state_path
     w = dict(WORKLOAD)
     if args.batch is not None:
@@ -531,36 +531,44 @@ def run_forward(args, rank, world, local):
     x, B, C, dt, A, bias, D = d["x"], d["B"], d["C"], d["dt"], d["A"], d["dt_bias"], d["D"].to(torch.bfloat16)
 
     def step(ev=None):
+        # the forward as `_mamba_chunk_scan_combined_fwd_concurrent` of this library runs it: two launches
         if ev:
             ev[0].record()
-        cb = bmm(C, B, L, output_dtype=torch.float32)
-        if ev:
-            ev[1].record()
         dA, dto, passed, fin = state_path(dt, A, B, x, L, torch.bfloat16, dt_bias=bias, dt_softplus=True)
         if ev:
-            ev[2].record()
-        y, _ = scan(cb, x, dto, dA, C, passed, D=D)
+            ev[1].record()
+        y, _ = bmm_scan(C, B, x, dto, dA, passed, D=D)
         if ev:
-            ev[3].record()
-        return y, fin
+            ev[2].record()
+        return y, fin, dA, dto, passed
 
     ms = _timed_steps(step, args.steps, args.warmup, None, dev)
     Kp = max(3, min(args.steps, 20))
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(Kp)]
     for e in evs:
-        step(e)
+        y, fin, dA, dto, passed = step(e)
     torch.cuda.synchronize()
-    names = ["bmm_chunk_ms", "state_path_ms", "chunk_scan_ms"]
+    names = ["state_path_ms", "bmm_chunk_scan_one_kernel_ms"]
     kernels = {n: statistics.median(e[i].elapsed_time(e[i + 1]) for e in evs) for i, n in enumerate(names)}
+    # the two separate kernels of the reference's call surface, for comparison
+    for e in evs:
+        e[0].record()
+        cb = bmm(C, B, L, output_dtype=torch.float32)
+        e[1].record()
+        scan(cb, x, dto, dA, C, passed, D=D)
+        e[2].record()
+    torch.cuda.synchronize()
+    kernels["bmm_chunk_ms"] = statistics.median(e[0].elapsed_time(e[1]) for e in evs)
+    kernels["chunk_scan_ms"] = statistics.median(e[1].elapsed_time(e[2]) for e in evs)
     from mamba_fused_minimal_b200._ext import C as _C
     _C.check_status(x)
     if rank == 0:
         print(json.dumps({"metric": "ssd_forward_tokens_per_s", "value": w["batch"] * w["seqlen"] / (ms * 1e-3),
                           "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
                           "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-                          "config": dict(workload=w["name"] + " forward (bmm, state path, chunk scan)",
+                          "config": dict(workload=w["name"] + " forward (state path, chunk bmm + chunk scan)",
                                          **{k: v for k, v in w.items() if k != "name"}),
-                          "kernels": kernels, "gpu_launches": 3 * args.steps}), flush=True)
+                          "kernels": kernels, "gpu_launches": 2 * args.steps}), flush=True)
 
 
 def run_seq1m(args, rank, world, local):

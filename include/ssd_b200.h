@@ -337,9 +337,8 @@ SSD_API int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t 
  *    Only the tcgen05 kernel implements this: 16-bit inputs, headdim 64, dstate 128, chunk size
  *    128 or 256, no seq_idx, 16-byte aligned tensors with contiguous innermost dimensions.  For
  *    anything else the call returns SSD_ERR_UNSUPPORTED and enqueues nothing; the caller then makes
- *    the two separate calls (5) and (6).  Results agree with the two calls within the output
- *    type's rounding (below the diagonal the decay factor is applied as two multiplications, see
- *    the kernel; the rounding point before the dot product is the same).
+ *    the two separate calls (5) and (6).  Same operations in the same order as the two calls: a
+ *    few outputs per million differ from theirs, by one step of the 16-bit output type.
  * ---------------------------------------------------------------------------------- */
 typedef struct {
   ssd_chunk_scan_params_t scan;
@@ -348,6 +347,24 @@ typedef struct {
 } ssd_chunk_scan_fused_params_t;
 
 SSD_API int ssd_chunk_scan_fused_fwd(const ssd_chunk_scan_fused_params_t* prm, ssd_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * 6b. the whole forward in one call.  Replaces the body of
+ *    _mamba_chunk_scan_combined_fwd_concurrent (main.py:93-103 of the reference: chunk bmm, chunk
+ *    cumsum, fused chunk state + state passing, chunk scan -- four launches there): here the state
+ *    path (4a) and the chunk bmm + chunk scan (6a) are enqueued back to back on `stream`, TWO
+ *    launches when both tcgen05 kernels take the problem, and cb never exists.
+ *    `path` and `scan` are read exactly as by ssd_state_path_fwd and ssd_chunk_scan_fused_fwd; the
+ *    caller points scan.scan.dt / dA_cumsum at path.cumsum.dt_out / dA_cumsum and scan.scan.states at
+ *    path.fused.out.  If the scan part is not supported (SSD_ERR_UNSUPPORTED, see 6a) nothing is
+ *    enqueued.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  ssd_state_path_params_t path;
+  ssd_chunk_scan_fused_params_t scan;
+} ssd_combined_params_t;
+
+SSD_API int ssd_combined_fwd(const ssd_combined_params_t* prm, ssd_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * 7. sequence-parallel fix-up.  No counterpart in the reference (it is single-GPU,

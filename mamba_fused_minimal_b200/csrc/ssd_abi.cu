@@ -347,4 +347,15 @@ int ssd_chunk_scan_fused_fwd(const ssd_chunk_scan_fused_params_t* prm, ssd_strea
   return launch_chunk_scan_fused(*prm, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int ssd_combined_fwd(const ssd_combined_params_t* prm, ssd_stream_t stream) {
+  SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
+  SSD_REQUIRE(prm->scan.B != nullptr && prm->scan.scan.x != nullptr && prm->scan.scan.C != nullptr, SSD_ERR_BAD_ARGUMENT,
+              "B, x and C must not be NULL");
+  SSD_REQUIRE(scan_fused_ok(prm->scan), SSD_ERR_UNSUPPORTED,
+              "the fused chunk bmm + chunk scan kernel does not take this problem: make the separate calls");
+  const int rc = ssd_state_path_fwd(&prm->path, stream);
+  if (rc != SSD_OK) return rc;
+  return ssd_chunk_scan_fused_fwd(&prm->scan, stream);
+}
+
 }  // extern "C"

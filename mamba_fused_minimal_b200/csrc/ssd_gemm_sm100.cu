@@ -499,13 +499,14 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
 //     long before it is needed.
 //   * Units are 64 positions wide (four per 256-position chunk): half as many hand-offs between the
 //     row threads and the MMA thread as with 32.
-//   * Below the diagonal the decay is applied in factors: exp(a_m - a_k) dt_k =
-//     exp(a_m - a_e) * [exp(a_e - a_k) dt_k] with e the unit's last position.  The bracket is one
-//     vector per chunk (built once per CTA), the first factor one exp per row and unit: two
-//     multiplications per (m, k) pair instead of an exp and four operations.  Both exponents are <= 0
-//     there (a is non-increasing), so nothing overflows.  In the unit that holds the diagonal, and in
-//     a chunk whose cumulative sums are not non-increasing (positive A), every pair is evaluated as
-//     exp(min(a_m - a_k, 0)) dt_k exactly like the other kernel.
+//   * The decay, dt and causal mask are applied with the same operations in the same order as in
+//     chunk_scan_kernel and the products accumulate in the same order of positions: against
+//     _bmm_chunk_fwd followed by _chunk_scan_fwd a few outputs per million differ, by one step of the
+//     16-bit output type (measured 4 of 524 288; the fp32 accumulators agree to a bit or two and the
+//     final rounding falls on the other side).  (Applying the decay
+//     below the diagonal as two multiplications, exp(a_m - a_e) times a per-chunk vector
+//     exp(a_e - a_k) dt_k, was measured: 3 % faster, one element in 10^5 a 16-bit step apart; the
+//     exact form is kept.)
 //   * TMA and MMA issue are two threads in two warps: neither waits for the other's barriers.
 constexpr int kFsU = 64;               // positions per unit
 constexpr int kFsBSlots = 2;           // ring of B tiles (released by the cb MMAs)
@@ -528,10 +529,9 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
   constexpr uint32_t kBTile = 2 * kBBox, kXTile = kFsU * 128;                 // 16 KiB, 8 KiB
   constexpr uint32_t kOffS = 2 * kCBox, kOffB = kOffS + 2 * kSBox, kOffX = kOffB + kFsBSlots * kBTile;
   constexpr uint32_t kOffVec = kOffX + kFsXSlots * kXTile;
-  constexpr uint32_t kOffCtl = kOffVec + 3 * 256 * 4;
+  constexpr uint32_t kOffCtl = kOffVec + 2 * 256 * 4;
   float* dA_s = reinterpret_cast<float*>(smem + kOffVec);
   float* dt_s = dA_s + 256;
-  float* cv_s = dt_s + 256;                      // exp(a_e - a_k) * dt_k, e = last position of k's unit
   const uint32_t bars = sbase + kOffCtl;
   const uint32_t bar_cs = bars, bar_acc = bars + 8, bar_cb_full = bars + 16, bar_cb_free = bars + 24;
   auto bar_b_full = [&](int i) { return bars + 32 + 8u * i; };
@@ -596,16 +596,6 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  // per-position factor of the factored form, and whether this chunk allows it
-  int bad = 0;
-  if (warp < kScanRowWarps) {
-    for (int k = tid; k < L; k += kScanRowWarps * 32) {
-      const float ak = dA_s[k];
-      cv_s[k] = fast_exp(dA_s[k | (kFsU - 1)] - ak) * dt_s[k];
-      if (k > 0 && !(ak <= dA_s[k - 1])) bad = 1;
-    }
-  }
-  const bool exact_only = __syncthreads_or(bad) != 0;
   const uint32_t tmem_base = static_cast<uint32_t>(ctl[1]);
   constexpr uint32_t kAcc1 = 0, kAcc2 = 64, kCB = 128, kA2 = 192;     // TMEM columns: one cb block of 64, two A2 slots of 32
 
@@ -708,44 +698,30 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
 #pragma unroll
         for (int i = 0; i < 16; ++i) o[i] = 0u;
       } else {
-        if (u == udiag || exact_only) {
-          // cb * exp(min(a_m - a_k, 0)) * dt_k, two positions per instruction
+        // cb * exp(min(a_m - a_k, 0)) * dt_k, two positions per instruction (packed fp32): the same IEEE
+        // operations in the same order as one element at a time
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 t = *reinterpret_cast<const float4*>(dA_s + k0 + i);
-            const float4 d = *reinterpret_cast<const float4*>(dt_s + k0 + i);
-            const float ak[4] = {t.x, t.y, t.z, t.w}, dk[4] = {d.x, d.y, d.z, d.w};
+        for (int i = 0; i < 32; i += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(dA_s + k0 + i);
+          const float4 d = *reinterpret_cast<const float4*>(dt_s + k0 + i);
+          const float ak[4] = {t.x, t.y, t.z, t.w}, dk[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
-            for (int jj = 0; jj < 4; jj += 2) {
-              float2 dl = __ffma2_rn(make_float2(ak[jj], ak[jj + 1]), make_float2(-1.0f, -1.0f), make_float2(am, am));
-              dl.x = fminf(dl.x, 0.0f);
-              dl.y = fminf(dl.y, 0.0f);
-              dl = __fmul2_rn(dl, make_float2(1.4426950408889634f, 1.4426950408889634f));
-              const float2 e = make_float2(ex2_approx(dl.x), ex2_approx(dl.y));
-              float2 w = __fmul2_rn(make_float2(v[i + jj], v[i + jj + 1]), e);
-              w = __fmul2_rn(w, make_float2(dk[jj], dk[jj + 1]));
-              v[i + jj] = w.x;
-              v[i + jj + 1] = w.y;
-            }
+          for (int jj = 0; jj < 4; jj += 2) {
+            float2 dl = __ffma2_rn(make_float2(ak[jj], ak[jj + 1]), make_float2(-1.0f, -1.0f), make_float2(am, am));
+            dl.x = fminf(dl.x, 0.0f);
+            dl.y = fminf(dl.y, 0.0f);
+            dl = __fmul2_rn(dl, make_float2(1.4426950408889634f, 1.4426950408889634f));
+            const float2 e = make_float2(ex2_approx(dl.x), ex2_approx(dl.y));
+            float2 w = __fmul2_rn(make_float2(v[i + jj], v[i + jj + 1]), e);
+            w = __fmul2_rn(w, make_float2(dk[jj], dk[jj + 1]));
+            v[i + jj] = w.x;
+            v[i + jj + 1] = w.y;
           }
-          if (u == udiag) {
+        }
+        if (u == udiag) {                              // the diagonal runs through this unit
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (k0 + i > m) v[i] = 0.0f;
-          }
-        } else {
-          // (cb * exp(a_m - a_e)) * [exp(a_e - a_k) * dt_k]
-          const float rm = fast_exp(am - dA_s[u * kFsU + kFsU - 1]);
-          const float2 rm2 = make_float2(rm, rm);
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 cvv = *reinterpret_cast<const float4*>(cv_s + k0 + i);
-            float2 w0 = __fmul2_rn(make_float2(v[i], v[i + 1]), rm2);
-            float2 w1 = __fmul2_rn(make_float2(v[i + 2], v[i + 3]), rm2);
-            w0 = __fmul2_rn(w0, make_float2(cvv.x, cvv.y));
-            w1 = __fmul2_rn(w1, make_float2(cvv.z, cvv.w));
-            v[i] = w0.x; v[i + 1] = w0.y; v[i + 2] = w1.x; v[i + 3] = w1.y;
-          }
+          for (int i = 0; i < 32; ++i)
+            if (k0 + i > m) v[i] = 0.0f;
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) o[i] = PackPair<T>::pack(v[2 * i], v[2 * i + 1]);
@@ -1047,7 +1023,7 @@ int launch_chunk_scan_fused(const ssd_chunk_scan_fused_params_t& f, cudaStream_t
   a.nchunks = nchunks;
   a.wait_limit = wait_limit_cycles();
   const int smem = 2 * kScanRows * 128 + 2 * kScanP * 128 + kFsBSlots * 2 * kFsU * 128 + kFsXSlots * kFsU * 128 +
-                   3 * 256 * 4 + 256 + 1024;
+                   2 * 256 * 4 + 256 + 1024;
   auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_fused_kernel<__nv_bfloat16> : chunk_scan_fused_kernel<__half>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);

@@ -72,8 +72,8 @@ def test_chunk_scan_fast_and_plain_kernels_agree(cuda_device):
                                                       (2, 384, 2, 2, 128, False, False), (1, 130, 2, 1, 128, False, True)])
 def test_bmm_chunk_scan_one_kernel_against_oracle_and_two_calls(cuda_device, dtype, b, l, h, g, L, d_hdim, with_d):
     """The kernel that computes C . B^T on chip against the oracle (atol = rtol = 1e-2 of the tensor's
-    max) and against `_bmm_chunk_fwd` + `_chunk_scan_fwd` (same rounding point; the decay below the
-    diagonal is applied as two multiplications, so the two agree to a bf16 step on rare elements)."""
+    max) and against `_bmm_chunk_fwd` + `_chunk_scan_fwd`: same products, same operations in the same
+    order."""
     from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _bmm_chunk_scan_fwd, _chunk_scan_fwd
     inp, d, dA, dt, passed, cb, D = _case(cuda_device, dtype, b, l, h, g, L, seed=l + h, d_hdim=d_hdim, with_d=with_d)
     Dd = None if D is None else D.to(cuda_device)
@@ -83,16 +83,18 @@ def test_bmm_chunk_scan_one_kernel_against_oracle_and_two_calls(cuda_device, dty
     scale = ref.float().abs().max()
     torch.testing.assert_close(out.float().cpu() / scale, ref.float() / scale, atol=1e-2, rtol=1e-2)
     assert torch.isfinite(out).all()
-    diff = (out.float() - two.float()).abs().max().item() / scale.item()
-    assert diff <= 2.0 ** -7, diff
-    assert (out == two).float().mean().item() > 0.99
+    # a handful of elements per million end up one 16-bit step apart (the fp32 accumulators agree to
+    # their last bit or two; the final rounding then falls on the other side)
+    assert (out == two).float().mean().item() >= 0.9999
+    step = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    assert ((out.float() - two.float()).abs() <= step * two.float().abs() + 1e-6 * scale.item()).all()
     from mamba_fused_minimal_b200._ext import C
     C.check_status(d["x"])
 
 
 def test_bmm_chunk_scan_one_kernel_gate_and_fast_decay(cuda_device):
     """z gating through the one-kernel route, and decays so fast that the factors underflow
-    (nothing may turn into NaN or infinity: both exponents of the factored form are <= 0)."""
+    (nothing may turn into NaN or infinity)."""
     from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _bmm_chunk_scan_fwd
     dtype = torch.bfloat16
     inp, d, dA, dt, passed, cb, D = _case(cuda_device, dtype, 2, 700, 4, 2, 256, seed=11)
@@ -113,8 +115,7 @@ def test_bmm_chunk_scan_one_kernel_gate_and_fast_decay(cuda_device):
 
 
 def test_bmm_chunk_scan_one_kernel_increasing_cumsum(cuda_device):
-    """Positive A makes the cumulative sums increase; the clamp exp(min(a_m - a_k, 0)) then matters and
-    the kernel must take its exact path for every unit."""
+    """Positive A makes the cumulative sums increase; the clamp exp(min(a_m - a_k, 0)) then matters."""
     from mamba_fused_minimal_b200.kernels.ssd_chunk_scan import _bmm_chunk_scan_fwd
     dtype = torch.bfloat16
     inp, d, dA, dt, passed, cb, D = _case(cuda_device, dtype, 1, 512, 2, 1, 256, seed=5)
