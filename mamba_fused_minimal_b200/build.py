@@ -3,6 +3,7 @@
   libssd_b200.so   the C-ABI library: hand-written CUDA for sm_100a (nvcc, static cudart)
   _C.so            the PyTorch C++ front end (g++ against the torch headers), linked to
                    libssd_b200.so through an $ORIGIN rpath
+  tma_copy_probe   a stand-alone diagnostic binary (how fast the state kernel's tiles move with TMA alone)
 
 Both land next to this file so that they travel with the source tree.  Nothing is built at
 import time on a machine without the toolchain: `mamba_fused_minimal_b200._ext` loads the
@@ -28,7 +29,8 @@ LIB = os.path.join(PKG, "libssd_b200.so")
 EXT = os.path.join(PKG, "_C.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--use_fast_math=false"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+PROBE = os.path.join(PKG, "tma_copy_probe")
 
 
 def _nvcc():
@@ -71,7 +73,7 @@ def _run(cmd, verbose):
 def build_lib(force=False, verbose=False):
     srcs = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
     hdrs = [h if os.path.isabs(h) else os.path.join(CSRC, h) for h in CUDA_HEADERS]
-    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + os.environ.get("SSD_EXTRA_NVCC_FLAGS", "").split()
+    flags = NVCC_FLAGS + os.environ.get("SSD_EXTRA_NVCC_FLAGS", "").split()
     stamp = _digest(srcs + hdrs, " ".join(flags))
     if not force and not _stale(LIB, stamp):
         return LIB
@@ -119,9 +121,22 @@ def build_ext(force=False, verbose=False):
     return EXT
 
 
+def build_probe(force=False, verbose=False):
+    """The stand-alone copy-engine probe (csrc/tma_copy_probe.cu): what the state kernel's tiles cost to
+    move with TMA alone.  A diagnostic for the roofline discussion; nothing in the library uses it."""
+    src = os.path.join(CSRC, "tma_copy_probe.cu")
+    stamp = _digest([src])
+    if not force and not _stale(PROBE, stamp):
+        return PROBE
+    _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", PROBE, src, "-lcuda"], verbose)
+    _write_stamp(PROBE, stamp)
+    return PROBE
+
+
 def build_all(force=False, verbose=False):
     build_lib(force, verbose)
     build_ext(force, verbose)
+    build_probe(force, verbose)
 
 
 if __name__ == "__main__":
