@@ -139,6 +139,13 @@ struct Cfg {
   static constexpr bool REBALANCE = true;
   static_assert(EPI_WARPS * REGS_EPI + SERVICE_WARPS * REGS_SERVICE + SCALE_WARPS * REGS_SCALE <= WARPS * LAUNCH_REGS,
                 "per-role register counts exceed the launch allocation");
+  // The register file is four files of 16 384, one per scheduler, and a warp lives in file (warp index % 4):
+  // the budget has to hold in each of them.  Every role is a multiple of four consecutive warps, so each
+  // file gets the same share of every role.  (This is also why a 21st warp cannot be added: the file that
+  // takes a sixth warp caps all threads at 80 registers, and the compiler then builds the kernel for 80.)
+  static_assert(WARPS % 4 == 0 && EPI_WARPS % 4 == 0 && SERVICE_WARPS % 4 == 0 && SCALE_WARPS % 4 == 0 &&
+                    (WARPS / 4) * LAUNCH_REGS * 32 <= 16384,
+                "roles must spread evenly over the four register files");
   static_assert(REGS_SCALE <= LAUNCH_REGS && REGS_SERVICE <= LAUNCH_REGS && REGS_EPI >= LAUNCH_REGS,
                 "scaling and service roles give registers back, the epilogue takes them");
 };
@@ -1156,6 +1163,24 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
                     : (seq ? fused_state_kernel<T, HPC, false, true, false> : fused_state_kernel<T, HPC, false, false, false>);
   if (raw != nullptr) kern = out32 ? fused_state_kernel<T, HPC, true, false, true> : fused_state_kernel<T, HPC, false, false, true>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  // setmaxnreg.inc waits, without a limit, for registers that the other roles give back: the per-role
+  // budgets only add up if the kernel was built with exactly the register count they were planned for
+  if (C::REBALANCE) {
+    static std::mutex mu;
+    static const void* checked[16];
+    static int nchecked = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    bool seen = false;
+    for (int i = 0; i < nchecked; ++i) seen = seen || checked[i] == reinterpret_cast<const void*>(kern);
+    if (!seen) {
+      cudaFuncAttributes fa;
+      SSD_CUDA_OK(cudaFuncGetAttributes(&fa, kern));
+      SSD_REQUIRE(fa.numRegs == C::LAUNCH_REGS, SSD_ERR_CUDA,
+                  "fused_state_kernel was built with %d registers per thread, its role budgets need %d", fa.numRegs,
+                  C::LAUNCH_REGS);
+      if (nchecked < 16) checked[nchecked++] = reinterpret_cast<const void*>(kern);
+    }
+  }
   // A strip longer than a CTA's range would make the CTAs of that strip wait for one another
   // in turn; then the carry is deferred to a second, small kernel instead.
   // (Only when the ranges are long: for short ones the chained carry costs next to nothing and
