@@ -5,6 +5,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "ssd_common.cuh"
 #include "ssd_launch.h"
 
@@ -27,6 +29,15 @@ long long wait_limit_cycles() { return g_wait_limit_cycles.load(std::memory_orde
 int debug_flags() { return g_debug_flags.load(std::memory_order_relaxed); }
 
 namespace {
+
+// One NVTX range per entry point (host side: validation, tensor maps, launches), visible in any
+// tool that attaches to NVTX; without a tool the calls return at once.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 int check_state_inputs(const ssd_state_inputs_t& in) {
   SSD_REQUIRE(in.x && in.B && in.dt && in.dA_cumsum, SSD_ERR_BAD_ARGUMENT, "x, B, dt and dA_cumsum must not be NULL");
@@ -63,6 +74,7 @@ const char* ssd_last_error(void) { return get_error(); }
 int ssd_abi_version(void) { return SSD_B200_ABI_VERSION; }
 
 int ssd_chunk_cumsum_fwd(const ssd_chunk_cumsum_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_chunk_cumsum_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_chunk_cumsum_params_t& p = *prm;
   SSD_REQUIRE(p.dt && p.A && p.dt_out && p.dA_cumsum, SSD_ERR_BAD_ARGUMENT, "dt, A, dt_out and dA_cumsum must not be NULL");
@@ -74,6 +86,7 @@ int ssd_chunk_cumsum_fwd(const ssd_chunk_cumsum_params_t* prm, ssd_stream_t stre
 }
 
 int ssd_chunk_state_fwd(const ssd_chunk_state_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_chunk_state_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_chunk_state_params_t& p = *prm;
   int rc = check_state_inputs(p.in);
@@ -94,6 +107,7 @@ int ssd_chunk_state_fwd(const ssd_chunk_state_params_t* prm, ssd_stream_t stream
 }
 
 int ssd_state_passing_fwd(const ssd_state_passing_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_state_passing_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_state_passing_params_t& p = *prm;
   SSD_REQUIRE(p.states && p.dA_chunk_cumsum && p.out && p.final_states, SSD_ERR_BAD_ARGUMENT,
@@ -115,6 +129,7 @@ size_t ssd_fused_state_workspace_bytes(const ssd_fused_state_params_t* prm) {
 }
 
 int ssd_fused_state_fwd(const ssd_fused_state_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_fused_state_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_fused_state_params_t& p = *prm;
   int rc = check_state_inputs(p.in);
@@ -219,6 +234,7 @@ size_t ssd_state_path_workspace_bytes(const ssd_state_path_params_t* prm) {
 }
 
 int ssd_state_path_fwd(const ssd_state_path_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_state_path_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_chunk_cumsum_params_t& c = prm->cumsum;
   SSD_REQUIRE(c.dt && c.A && c.dt_out && c.dA_cumsum, SSD_ERR_BAD_ARGUMENT, "dt, A, dt_out and dA_cumsum must not be NULL");
@@ -292,6 +308,7 @@ int ssd_check_status(void* workspace, ssd_stream_t stream) {
 }
 
 int ssd_seqpar_fixup(const ssd_seqpar_fixup_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_seqpar_fixup");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_seqpar_fixup_params_t& p = *prm;
   SSD_REQUIRE(p.Z_all && p.logP_all && p.dA_chunk_last && p.out && p.final_states, SSD_ERR_BAD_ARGUMENT,
@@ -304,6 +321,7 @@ int ssd_seqpar_fixup(const ssd_seqpar_fixup_params_t* prm, ssd_stream_t stream) 
 }
 
 int ssd_bmm_chunk_fwd(const ssd_bmm_chunk_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_bmm_chunk_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_bmm_chunk_params_t& p = *prm;
   SSD_REQUIRE(p.a && p.b && p.out, SSD_ERR_BAD_ARGUMENT, "a, b and out must not be NULL");
@@ -315,6 +333,7 @@ int ssd_bmm_chunk_fwd(const ssd_bmm_chunk_params_t* prm, ssd_stream_t stream) {
 }
 
 int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_chunk_scan_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_chunk_scan_params_t& p = *prm;
   SSD_REQUIRE(p.cb && p.x && p.dt && p.dA_cumsum && p.C && p.states && p.out, SSD_ERR_BAD_ARGUMENT,
@@ -331,6 +350,7 @@ int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t stream) 
 }
 
 int ssd_chunk_scan_fused_fwd(const ssd_chunk_scan_fused_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_chunk_scan_fused_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   const ssd_chunk_scan_params_t& p = prm->scan;
   SSD_REQUIRE(prm->B && p.x && p.dt && p.dA_cumsum && p.C && p.states && p.out, SSD_ERR_BAD_ARGUMENT,
@@ -348,6 +368,7 @@ int ssd_chunk_scan_fused_fwd(const ssd_chunk_scan_fused_params_t* prm, ssd_strea
 }
 
 int ssd_combined_fwd(const ssd_combined_params_t* prm, ssd_stream_t stream) {
+  NvtxRange nvtx_range("ssd_combined_fwd");
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   SSD_REQUIRE(prm->scan.B != nullptr && prm->scan.scan.x != nullptr && prm->scan.scan.C != nullptr, SSD_ERR_BAD_ARGUMENT,
               "B, x and C must not be NULL");

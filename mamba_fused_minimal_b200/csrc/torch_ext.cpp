@@ -117,6 +117,65 @@ Tensor get_workspace(const Tensor& like, size_t bytes, ssd_stream_t stream) {
 }
 
 // ---------------------------------------------------------------------------------------
+// Guard bands (debug mode; the stand-in for a memory checker on machines where none can run).
+// With debug_set_guard_bytes(n > 0) every output the front end allocates is the middle of a
+// larger buffer whose first and last n bytes hold a canary pattern; debug_check_guards()
+// synchronises, counts the outputs allocated since the last check whose bands no longer hold
+// the pattern (a kernel wrote outside its tensor) and forgets them.  Reads outside a tensor
+// are caught from the other side by the tests: inputs placed between bands of NaNs.
+constexpr uint8_t kCanary = 0xA5;
+std::mutex g_guard_mutex;
+int64_t g_guard_bytes = 0;
+struct Guarded {
+  Tensor buf;
+  int64_t payload;
+};
+std::vector<Guarded> g_guarded;
+
+Tensor alloc_out(at::IntArrayRef sizes, const at::TensorOptions& opts) {
+  int64_t guard;
+  {
+    std::lock_guard<std::mutex> lock(g_guard_mutex);
+    guard = g_guard_bytes;
+  }
+  if (guard == 0) return torch::empty(sizes, opts);
+  int64_t numel = 1;
+  for (int64_t d : sizes) numel *= d;
+  const int64_t payload = numel * (int64_t)c10::elementSize(c10::typeMetaToScalarType(opts.dtype()));
+  const int64_t padded = (payload + 255) / 256 * 256;
+  Tensor buf = torch::full({guard + padded + guard}, kCanary, torch::dtype(torch::kUInt8).device(opts.device()));
+  Tensor out = buf.narrow(0, guard, payload).view(c10::typeMetaToScalarType(opts.dtype())).view(sizes);
+  std::lock_guard<std::mutex> lock(g_guard_mutex);
+  g_guarded.push_back({buf, payload});
+  return out;
+}
+
+void debug_set_guard_bytes(int64_t bytes) {
+  TORCH_CHECK(bytes >= 0 && bytes % 256 == 0, "guard bytes must be a non-negative multiple of 256");
+  std::lock_guard<std::mutex> lock(g_guard_mutex);
+  g_guard_bytes = bytes;
+}
+
+int64_t debug_check_guards() {
+  std::vector<Guarded> list;
+  {
+    std::lock_guard<std::mutex> lock(g_guard_mutex);
+    list.swap(g_guarded);
+  }
+  int64_t damaged = 0;
+  for (Guarded& g : list) {
+    c10::cuda::CUDAGuard guard(g.buf.device());
+    const int64_t total = g.buf.numel();
+    const int64_t band = (total - (g.payload + 255) / 256 * 256) / 2;
+    const bool front = g.buf.narrow(0, 0, band).eq(kCanary).all().item<bool>();
+    // the bytes between the payload's end and the next multiple of 256 belong to the back band
+    const bool back = g.buf.narrow(0, band + g.payload, total - band - g.payload).eq(kCanary).all().item<bool>();
+    if (!front || !back) ++damaged;
+  }
+  return damaged;
+}
+
+// ---------------------------------------------------------------------------------------
 std::tuple<Tensor, Tensor> chunk_cumsum_fwd(const Tensor& dt, const Tensor& A, int64_t chunk_size,
                                             const OptTensor& dt_bias, bool dt_softplus, double dt_min,
                                             double dt_max) {
@@ -127,8 +186,8 @@ std::tuple<Tensor, Tensor> chunk_cumsum_fwd(const Tensor& dt, const Tensor& A, i
   const int64_t batch = dt.size(0), seqlen = dt.size(1), nheads = dt.size(2);
   const int64_t nchunks = (seqlen + chunk_size - 1) / chunk_size;
   auto opts = torch::dtype(torch::kFloat).device(dt.device());
-  Tensor dt_out = torch::empty({batch, nheads, nchunks, chunk_size}, opts);
-  Tensor dA_cumsum = torch::empty({batch, nheads, nchunks, chunk_size}, opts);
+  Tensor dt_out = alloc_out({batch, nheads, nchunks, chunk_size}, opts);
+  Tensor dA_cumsum = alloc_out({batch, nheads, nchunks, chunk_size}, opts);
   ssd_chunk_cumsum_params_t p{};
   p.dt = dt.data_ptr();
   p.A = A.data_ptr();
@@ -170,7 +229,7 @@ Tensor chunk_state_fwd(const Tensor& B, const Tensor& x, const Tensor& dt, const
     states = *states_in;
     check_cuda(states, x, "states");
   } else {
-    states = torch::empty({x.size(0), nchunks, x.size(2), x.size(3), B.size(3)},
+    states = alloc_out({x.size(0), nchunks, x.size(2), x.size(3), B.size(3)},
                           torch::dtype(states_in_fp32 ? at::kFloat : B.scalar_type()).device(x.device()));
   }
   p.states = states.data_ptr();
@@ -189,8 +248,8 @@ std::tuple<Tensor, Tensor> state_passing_fwd(const Tensor& states, const Tensor&
   c10::cuda::CUDAGuard guard(states.device());
   const int64_t batch = states.size(0), nchunks = states.size(1), nheads = states.size(2), dim = states.size(3);
   const at::ScalarType odt = out_dtype.value_or(states.scalar_type());
-  Tensor out = torch::empty({batch, nchunks, nheads, dim}, torch::dtype(odt).device(states.device()));
-  Tensor fin = torch::empty({batch, nheads, dim}, torch::dtype(at::kFloat).device(states.device()));
+  Tensor out = alloc_out({batch, nchunks, nheads, dim}, torch::dtype(odt).device(states.device()));
+  Tensor fin = alloc_out({batch, nheads, dim}, torch::dtype(at::kFloat).device(states.device()));
   ssd_state_passing_params_t p{};
   p.states = states.data_ptr();
   p.states_dtype = dtype_code(states, "states");
@@ -245,7 +304,7 @@ std::tuple<Tensor, Tensor> fused_state_fwd(const Tensor& B, const Tensor& x, con
   const at::ScalarType states_dt = states_in.has_value() ? states_in->scalar_type()
                                                          : (states_in_fp32 ? at::kFloat : B.scalar_type());
   const at::ScalarType odt = out_dtype.value_or(states_dt);
-  Tensor out = torch::empty({batch, nchunks, nheads, headdim, dstate}, torch::dtype(odt).device(x.device()));
+  Tensor out = alloc_out({batch, nchunks, nheads, headdim, dstate}, torch::dtype(odt).device(x.device()));
   // final_out: a caller-owned place for the final states (e.g. a slot of an exchange buffer)
   Tensor fin;
   if (final_out.has_value()) {
@@ -255,7 +314,7 @@ std::tuple<Tensor, Tensor> fused_state_fwd(const Tensor& B, const Tensor& x, con
                     fin.size(2) == headdim && fin.size(3) == dstate && fin.stride(3) == 1,
                 "final_states must be fp32 (b, h, p, n) with a contiguous last dimension");
   } else {
-    fin = torch::empty({batch, nheads, headdim, dstate}, torch::dtype(at::kFloat).device(x.device()));
+    fin = alloc_out({batch, nheads, headdim, dstate}, torch::dtype(at::kFloat).device(x.device()));
   }
   if (initial_states.has_value()) {
     check_cuda(*initial_states, x, "initial_states");
@@ -308,8 +367,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> state_path_fwd(
               "dt, A, B and x disagree on batch / seqlen / nheads");
   const int64_t nchunks = (seqlen + chunk_size - 1) / chunk_size;
   auto f32 = torch::dtype(torch::kFloat).device(x.device());
-  Tensor dt_out = torch::empty({batch, nheads, nchunks, chunk_size}, f32);
-  Tensor dA_cumsum = torch::empty({batch, nheads, nchunks, chunk_size}, f32);
+  Tensor dt_out = alloc_out({batch, nheads, nchunks, chunk_size}, f32);
+  Tensor dA_cumsum = alloc_out({batch, nheads, nchunks, chunk_size}, f32);
   ssd_state_path_params_t p{};
   ssd_chunk_cumsum_params_t& c = p.cumsum;
   c.dt = dt.data_ptr();
@@ -343,7 +402,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> state_path_fwd(
   const at::ScalarType states_dt = states_in.has_value() ? states_in->scalar_type()
                                                          : (states_in_fp32 ? at::kFloat : B.scalar_type());
   const at::ScalarType odt = out_dtype.value_or(states_dt);
-  Tensor out = torch::empty({batch, nchunks, nheads, headdim, dstate}, torch::dtype(odt).device(x.device()));
+  Tensor out = alloc_out({batch, nchunks, nheads, headdim, dstate}, torch::dtype(odt).device(x.device()));
   Tensor fin;
   if (final_out.has_value()) {
     fin = *final_out;
@@ -352,7 +411,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> state_path_fwd(
                     fin.size(2) == headdim && fin.size(3) == dstate && fin.stride(3) == 1,
                 "final_states must be fp32 (b, h, p, n) with a contiguous last dimension");
   } else {
-    fin = torch::empty({batch, nheads, headdim, dstate}, f32);
+    fin = alloc_out({batch, nheads, headdim, dstate}, f32);
   }
   if (initial_states.has_value()) {
     check_cuda(*initial_states, x, "initial_states");
@@ -528,7 +587,7 @@ Tensor bmm_chunk_fwd(const Tensor& a, const Tensor& b, int64_t chunk_size, const
   const int64_t batch = a4.size(0), seqlen = a4.size(1), ngroups = a4.size(2), k = a4.size(3);
   const int64_t nchunks = (seqlen + chunk_size - 1) / chunk_size;
   const at::ScalarType odt = output_dtype.value_or(a.scalar_type());
-  Tensor out = torch::empty({batch, nchunks, ngroups, chunk_size, chunk_size}, torch::dtype(odt).device(a.device()));
+  Tensor out = alloc_out({batch, nchunks, ngroups, chunk_size, chunk_size}, torch::dtype(odt).device(a.device()));
   ssd_bmm_chunk_params_t p{};
   p.a = a4.data_ptr();
   p.b = b4.data_ptr();
@@ -564,7 +623,7 @@ std::tuple<Tensor, OptTensor> chunk_scan_fwd(const Tensor& cb, const Tensor& x, 
   TORCH_CHECK(C.scalar_type() == x.scalar_type(), "C and x must have the same dtype");
   TORCH_CHECK(dt.scalar_type() == at::kFloat && dA_cumsum.scalar_type() == at::kFloat, "dt and dA_cumsum must be fp32");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor out = torch::empty({x.size(0), x.size(1), x.size(2), x.size(3)}, x.options());
+  Tensor out = alloc_out({x.size(0), x.size(1), x.size(2), x.size(3)}, x.options());
   OptTensor out_x;
   ssd_chunk_scan_params_t p{};
   p.cb = cb.data_ptr();
@@ -606,7 +665,7 @@ std::tuple<Tensor, OptTensor> chunk_scan_fwd(const Tensor& cb, const Tensor& x, 
     zh = *z;
     p.z = zh.data_ptr();
     copy_strides(p.z_stride, zh, {0, 1, 2, 3});
-    out_x = torch::empty_like(out);
+    out_x = alloc_out(out.sizes(), out.options());
     p.out_x = out_x->data_ptr();
   }
   if (seq_idx.has_value()) {
@@ -636,7 +695,7 @@ std::tuple<Tensor, OptTensor> chunk_scan_combined_fwd(const Tensor& C, const Ten
   bool try_fused = !seq_idx.has_value();
   if (try_fused) {
     c10::cuda::CUDAGuard guard(x.device());
-    Tensor out = torch::empty({x.size(0), x.size(1), x.size(2), x.size(3)}, x.options());
+    Tensor out = alloc_out({x.size(0), x.size(1), x.size(2), x.size(3)}, x.options());
     OptTensor out_x;
     ssd_chunk_scan_fused_params_t f{};
     ssd_chunk_scan_params_t& p = f.scan;
@@ -679,7 +738,7 @@ std::tuple<Tensor, OptTensor> chunk_scan_combined_fwd(const Tensor& C, const Ten
       zh = *z;
       p.z = zh.data_ptr();
       copy_strides(p.z_stride, zh, {0, 1, 2, 3});
-      out_x = torch::empty_like(out);
+      out_x = alloc_out(out.sizes(), out.options());
       p.out_x = out_x->data_ptr();
     }
     const int rc = ssd_chunk_scan_fused_fwd(&f, current_stream(x));
@@ -722,6 +781,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("check_status", &check_status, py::arg("like"));
   m.def("debug_set_wait_limit_cycles", [](int64_t cycles) { ssd_debug_set_wait_limit_cycles((long long)cycles); });
   m.def("debug_set_flags", [](int64_t flags) { ssd_debug_set_flags((int)flags); });
+  m.def("debug_set_guard_bytes", &debug_set_guard_bytes, py::arg("bytes"));
+  m.def("debug_check_guards", &debug_check_guards);
   m.def("bmm_chunk_fwd", &bmm_chunk_fwd, py::arg("a"), py::arg("b"), py::arg("chunk_size"),
         py::arg("seq_idx") = py::none(), py::arg("causal") = false, py::arg("output_dtype") = py::none());
   m.def("chunk_scan_combined_fwd", &chunk_scan_combined_fwd, py::arg("C"), py::arg("B"), py::arg("x"), py::arg("dt"),

@@ -21,7 +21,9 @@ def test_header_declares_the_expected_entry_points():
     syms = declared_symbols()
     for s in ["ssd_chunk_cumsum_fwd", "ssd_chunk_state_fwd", "ssd_state_passing_fwd", "ssd_fused_state_fwd",
               "ssd_fused_state_workspace_bytes", "ssd_bmm_chunk_fwd", "ssd_chunk_scan_fwd", "ssd_check_status",
-              "ssd_last_error", "ssd_abi_version"]:
+              "ssd_last_error", "ssd_abi_version", "ssd_state_path_fwd", "ssd_state_path_workspace_bytes",
+              "ssd_chunk_scan_fused_fwd", "ssd_combined_fwd", "ssd_seqpar_fixup", "ssd_fused_state_fwd_static",
+              "ssd_debug_set_wait_limit_cycles", "ssd_debug_set_flags"]:
         assert s in syms
 
 
@@ -38,7 +40,8 @@ def test_null_params_are_rejected_with_a_message():
     lib = load_abi()
     lib.ssd_last_error.restype = ctypes.c_char_p
     for fn in ["ssd_chunk_cumsum_fwd", "ssd_chunk_state_fwd", "ssd_state_passing_fwd", "ssd_fused_state_fwd",
-               "ssd_bmm_chunk_fwd", "ssd_chunk_scan_fwd"]:
+               "ssd_bmm_chunk_fwd", "ssd_chunk_scan_fwd", "ssd_state_path_fwd", "ssd_chunk_scan_fused_fwd",
+               "ssd_combined_fwd", "ssd_seqpar_fixup", "ssd_fused_state_fwd_static"]:
         rc = getattr(lib, fn)(None, None)
         assert rc == 1, fn                       # SSD_ERR_BAD_ARGUMENT
         assert b"NULL" in lib.ssd_last_error()
