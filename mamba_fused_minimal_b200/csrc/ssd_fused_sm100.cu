@@ -1239,6 +1239,24 @@ int make_rows_map(CUtensorMap* map, const void* base, int dtype, int inner, int 
   return SSD_OK;
 }
 
+// A 16-bit (b, l, h, 64) tensor as the destination of per-warp stores: a box is 32 positions x 32 of
+// the 64 inner elements (32 rows of 64 bytes, 64-byte swizzle).  Rows past seqlen are clipped.
+int make_rows_store_map(CUtensorMap* map, const void* base, int dtype, int heads, int seqlen, int batch,
+                        const int64_t* stride /* b, l, h */) {
+  EncodeTiledFn enc = get_encode_fn();
+  SSD_REQUIRE(enc != nullptr, SSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[4] = {64, (cuuint64_t)heads, (cuuint64_t)seqlen, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)stride[2] * 2, (cuuint64_t)stride[1] * 2, (cuuint64_t)stride[0] * 2};
+  const cuuint32_t box[4] = {32, 1, 32, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == SSD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SSD_REQUIRE(r == CUDA_SUCCESS, SSD_ERR_CUDA, "cuTensorMapEncodeTiled (row stores) failed with CUresult %d", (int)r);
+  return SSD_OK;
+}
+
 int make_states_map(CUtensorMap* map, const void* base, int dtype, int nheads, int nchunks, int batch,
                     const int64_t* stride /* b, c, h */) {
   EncodeTiledFn enc = get_encode_fn();

@@ -215,7 +215,7 @@ template <typename T>
 __global__ void __launch_bounds__(kScanThreads, 2)
 chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_constant__ CUtensorMap tmap_S,
                   const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_cb,
-                  const ScanArgs a) {
+                  const __grid_constant__ CUtensorMap tmap_out, const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -424,7 +424,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
       tmem_ld_wait();
       float res[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) res[i] = __uint_as_float(r1[i]) * sm + __uint_as_float(r2[i]);
+      for (int i = 0; i < 32; ++i) res[i] = fmaf(__uint_as_float(r1[i]), sm, __uint_as_float(r2[i]));
       if (a.D != nullptr && live) {
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {             // 16-byte pieces = 8 headdim columns
@@ -436,8 +436,8 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
             const int pcol = q * 32 + pc * 8 + 2 * i;
             const float d0 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol) : dh;
             const float d1 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol + 1) : dh;
-            res[pc * 8 + 2 * i] += x0 * d0;
-            res[pc * 8 + 2 * i + 1] += x1 * d1;
+            res[pc * 8 + 2 * i] = fmaf(x0, d0, res[pc * 8 + 2 * i]);        // explicit: both scan kernels round alike
+            res[pc * 8 + 2 * i + 1] = fmaf(x1, d1, res[pc * 8 + 2 * i + 1]);
           }
         }
       }
@@ -463,7 +463,28 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
           }
         }
       }
-      if (live) {
+      if (a.z == nullptr) {
+        // Without a gate the result leaves through shared memory as one TMA store per warp: this warp's
+        // 32 rows x 32 columns as a 32 x 64-byte box (64-byte swizzle: piece c of row r at piece
+        // c ^ ((r / 2) % 4)) in the C tile's shared memory, which no MMA reads any more.
+        uint8_t* stg = smem + warp * (32 * 64);
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 t;
+          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
+          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
+          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
+          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
+          *reinterpret_cast<uint4*>(stg + lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4)) = t;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && mt * kScanRows + (warp & 3) * 32 < limit) {   // rows past the sequence end are clipped by the map
+          tma_store_4d(&tmap_out, sbase + warp * (32 * 64), q * 32, h, c * L + mt * kScanRows + (warp & 3) * 32, b);
+          bulk_commit();
+          bulk_wait_read_all();                                         // the CTA's shared memory goes away with it
+        }
+      } else if (live) {
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
           uint4 t;
@@ -518,7 +539,7 @@ template <typename T>
 __global__ void __launch_bounds__(kFsThreads, 2)
 chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_constant__ CUtensorMap tmap_S,
                         const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_B,
-                        const ScanArgs a) {
+                        const __grid_constant__ CUtensorMap tmap_out, const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -744,10 +765,24 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
     const int64_t pos = (int64_t)c * L + m;
     const uint8_t* xrow = static_cast<const uint8_t*>(a.x) +
                           2 * ((int64_t)b * a.x_s[0] + pos * a.x_s[1] + (int64_t)h * a.x_s[2]) + q * 64;
+    // Without a gate the row's x values come from the staged x tile of its unit (one of the last two
+    // units this CTA loaded, still in the ring: 128-byte rows, 16-byte pieces swizzled by the row index
+    // modulo 8) and the result leaves through shared memory as one TMA store per warp; with a gate the
+    // rows are read and written by their threads, 16 bytes at a time.
+    const bool staged = a.z == nullptr;
     uint4 xr[4];
     if (a.D != nullptr && live) {                    // requested before the wait, used after it
+      if (staged) {
+        const int ux = m / kFsU;
+        ok = mbar_wait(bar_x_full(ux % kFsXSlots), (ux / kFsXSlots) & 1, wc, kFsWaitXFull);
+        const uint32_t xs = sbase + kOffX + (ux % kFsXSlots) * kXTile + (m & (kFsU - 1)) * 128;
 #pragma unroll
-      for (int pc = 0; pc < 4; ++pc) xr[pc] = __ldg(reinterpret_cast<const uint4*>(xrow) + pc);
+        for (int pc = 0; pc < 4; ++pc)
+          xr[pc] = *reinterpret_cast<const uint4*>(smem + (xs - sbase) + (((q * 4 + pc) ^ (m & 7)) << 4));
+      } else {
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) xr[pc] = __ldg(reinterpret_cast<const uint4*>(xrow) + pc);
+      }
     }
     uint4 zr[4];
     if (a.z != nullptr && live) {
@@ -769,7 +804,7 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
       tmem_ld_wait();
       float res[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) res[i] = __uint_as_float(r1[i]) * sm + __uint_as_float(r2[i]);
+      for (int i = 0; i < 32; ++i) res[i] = fmaf(__uint_as_float(r1[i]), sm, __uint_as_float(r2[i]));
       if (a.D != nullptr && live) {
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {             // 16-byte pieces = 8 headdim columns
@@ -781,8 +816,8 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
             const int pcol = q * 32 + pc * 8 + 2 * i;
             const float d0 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol) : dh;
             const float d1 = a.D_has_hdim ? load_f(a.D, a.D_dtype, (int64_t)h * a.D_stride + pcol + 1) : dh;
-            res[pc * 8 + 2 * i] += x0 * d0;
-            res[pc * 8 + 2 * i + 1] += x1 * d1;
+            res[pc * 8 + 2 * i] = fmaf(x0, d0, res[pc * 8 + 2 * i]);        // explicit: both scan kernels round alike
+            res[pc * 8 + 2 * i + 1] = fmaf(x1, d1, res[pc * 8 + 2 * i + 1]);
           }
         }
       }
@@ -807,7 +842,27 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
           }
         }
       }
-      if (live) {
+      if (staged) {
+        // This warp's 32 rows x 32 columns as a 32 x 64-byte box (64-byte swizzle: piece c of row r at
+        // piece c ^ ((r / 2) % 4)) in the C tile's shared memory, which no MMA reads any more.
+        uint8_t* stg = smem + warp * (32 * 64);
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 t;
+          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
+          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
+          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
+          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
+          *reinterpret_cast<uint4*>(stg + lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4)) = t;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && mt * kScanRows + wq * 32 < limit) {     // rows past the sequence end are clipped by the map
+          tma_store_4d(&tmap_out, sbase + warp * (32 * 64), q * 32, h, c * L + mt * kScanRows + wq * 32, b);
+          bulk_commit();
+          bulk_wait_read_all();                                   // the CTA's shared memory goes away with it
+        }
+      } else if (live) {
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
           uint4 t;
@@ -962,7 +1017,10 @@ int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream
   auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_kernel<__nv_bfloat16> : chunk_scan_kernel<__half>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
-  kern<<<grid, kScanThreads, smem, stream>>>(mC, mS, mx, mcb, a);
+  CUtensorMap mo;
+  rc = make_rows_store_map(&mo, p.out, p.in_dtype, p.nheads, p.seqlen, p.batch, p.out_stride);
+  if (rc != SSD_OK) return rc;
+  kern<<<grid, kScanThreads, smem, stream>>>(mC, mS, mx, mcb, mo, a);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }
@@ -1027,7 +1085,10 @@ int launch_chunk_scan_fused(const ssd_chunk_scan_fused_params_t& f, cudaStream_t
   auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_fused_kernel<__nv_bfloat16> : chunk_scan_fused_kernel<__half>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
-  kern<<<grid, kFsThreads, smem, stream>>>(mC, mS, mx, mB, a);
+  CUtensorMap mo;
+  rc = make_rows_store_map(&mo, p.out, p.in_dtype, p.nheads, p.seqlen, p.batch, p.out_stride);
+  if (rc != SSD_OK) return rc;
+  kern<<<grid, kFsThreads, smem, stream>>>(mC, mS, mx, mB, mo, a);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }

@@ -55,6 +55,8 @@ int make_rows_map(CUtensorMap* map, const void* base, int dtype, int inner, int 
 
 // 5-D tensor map over 16-bit passed states (b, c, h, p, n) with (p, n) dense (strides in
 // elements: b, c, h); box = 64 n x 64 p, 128-byte swizzle.
+int make_rows_store_map(CUtensorMap* map, const void* base, int dtype, int heads, int seqlen, int batch,
+                        const int64_t* stride /* b, l, h */);
 int make_states_map(CUtensorMap* map, const void* base, int dtype, int nheads, int nchunks, int batch,
                     const int64_t* stride);
 
