@@ -521,13 +521,14 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
 //   * Units are 64 positions wide (four per 256-position chunk): half as many hand-offs between the
 //     row threads and the MMA thread as with 32.
 //   * The decay, dt and causal mask are applied with the same operations in the same order as in
-//     chunk_scan_kernel and the products accumulate in the same order of positions: against
-//     _bmm_chunk_fwd followed by _chunk_scan_fwd a few outputs per million differ, by one step of the
-//     16-bit output type (measured 4 of 524 288; the fp32 accumulators agree to a bit or two and the
-//     final rounding falls on the other side).  (Applying the decay
-//     below the diagonal as two multiplications, exp(a_m - a_e) times a per-chunk vector
-//     exp(a_e - a_k) dt_k, was measured: 3 % faster, one element in 10^5 a 16-bit step apart; the
-//     exact form is kept.)
+//     chunk_scan_kernel, the products accumulate in the same order of positions and the epilogues
+//     use the same explicit FMAs: the result carries the same bits as _bmm_chunk_fwd followed by
+//     _chunk_scan_fwd.  (Applying the decay below the diagonal as two multiplications,
+//     exp(a_m - a_e) times a per-chunk vector exp(a_e - a_k) dt_k, was measured: 3 % faster, one
+//     element in 10^5 a 16-bit step apart; the exact form is kept.)
+//   * Epilogue without a gate: the x values of the D term come from the staged x tiles (a row's unit
+//     is one of the last two this CTA loaded) and every warp sends its 32 x 32 piece of the output
+//     through shared memory as one TMA store.
 //   * TMA and MMA issue are two threads in two warps: neither waits for the other's barriers.
 constexpr int kFsU = 64;               // positions per unit
 constexpr int kFsBSlots = 2;           // ring of B tiles (released by the cb MMAs)
