@@ -213,8 +213,12 @@ SSD_API int ssd_check_status(void* workspace, ssd_stream_t stream);
  *   ssd_debug_set_flags: SSD_DEBUG_DROP_CARRY_FLAGS makes the fused kernel skip publishing its
  *     carry flags, so that a CTA which needs a carried state waits for a flag that nothing
  *     sets, runs into the limit and the call ends with SSD_ERR_TIMEOUT from ssd_check_status.
- *     This exists to test that path with a short limit; 0 restores normal operation. */
+ *     This exists to test that path with a short limit; 0 restores normal operation.
+ *     SSD_DEBUG_CUT_STRIPS makes the fused kernel always cut its work into one range per SM, also
+ *     where a problem has no more (batch, head pair) strips than SMs and would run one CTA per
+ *     strip: small test problems then exercise the carry chain between CTAs. */
 #define SSD_DEBUG_DROP_CARRY_FLAGS 1
+#define SSD_DEBUG_CUT_STRIPS 2
 SSD_API void ssd_debug_set_wait_limit_cycles(long long cycles);
 SSD_API void ssd_debug_set_flags(int flags);
 

@@ -1076,9 +1076,51 @@ int num_sms() {
   return sms[dev];
 }
 
+// How a problem is laid over the GPU: heads per CTA, CTAs, and whether the carry between the CTAs of a
+// strip is deferred to a second pass.  The chunks of a strip depend on one another, so cutting a strip
+// over several chained CTAs buys no time and costs the hand-offs; a CTA's time per chunk is set by its
+// own pipeline, hardly by how many other CTAs run (measured: 2.6 - 3.3 us per 256-position chunk alone,
+// 3.2 us with all SMs busy).  Hence, with S = SMs and H = batch x heads:
+//   * H <= S: one CTA per (batch, head), whole strips, one head per CTA -- twice as many SMs busy as with
+//     head pairs, no carries at all (the Mamba2-130M layer shape: 96 CTAs of 8 chunks, 29 us, where 148
+//     ranges of 2.6 chunks of head pairs, chained three or four deep, took 43 us);
+//   * H a little above S: one head per CTA, one range per SM (a range then holds a strip or more);
+//   * head pairs <= S: one CTA per (batch, head pair), whole strips;
+//   * more: head pairs, one contiguous range of (strip, chunk) items per SM, a range boundary inside a
+//     strip passes its state through a carry slot (the 2.7B layer shape and everything larger).
+//   * Few long strips (a range of 16 chunks or more that is still shorter than a strip): ranges per SM
+//     with the carry deferred to segment_fixup_kernel, whatever the above says; never with packed
+//     sequences.
+// Every layout does the same arithmetic per head: the results carry the same bits.  The states-only mode
+// has no recurrence: its items are independent and always cut per SM.
+struct FusedPlan {
+  int hpc, grid, defer;
+};
+
+FusedPlan plan_fused(const ssd_fused_state_params_t& p, int variant, int mode) {
+  const ssd_state_inputs_t& in = p.in;
+  const long long sms = std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas);
+  const long long nchunks = (in.seqlen + in.chunk_size - 1) / in.chunk_size;
+  auto cut = [&](int hpc) {
+    const long long total = (long long)in.batch * (in.nheads / hpc) * nchunks;
+    const long long grid = std::min(total, sms);
+    const long long per_cta = grid > 0 ? (total + grid - 1) / grid : 0;
+    const int defer = (mode == 0 && nchunks > per_cta && per_cta >= 16 && in.seq_idx == nullptr) ? 1 : 0;
+    return FusedPlan{hpc, (int)grid, defer};
+  };
+  const FusedPlan pairs = cut(variant);
+  if (mode != 0 || pairs.defer || (debug_flags() & SSD_DEBUG_CUT_STRIPS)) return pairs;
+  const long long heads = (long long)in.batch * in.nheads;
+  const FusedPlan singles = cut(1);
+  if (heads <= sms) return singles.defer ? pairs : FusedPlan{1, (int)heads, 0};
+  if (variant == 2 && heads <= sms + sms / 8 && !singles.defer) return singles;
+  if (heads / variant <= sms) return FusedPlan{variant, (int)(heads / variant), 0};
+  return pairs;
+}
+
 template <typename T, int HPC>
 int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t stream,
-                   const ssd_chunk_cumsum_params_t* raw) {
+                   const ssd_chunk_cumsum_params_t* raw, const FusedPlan& plan) {
   using C = Cfg<HPC>;
   const ssd_state_inputs_t& in = p.in;
   CUtensorMap mx, mB;
@@ -1154,8 +1196,7 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
   a.debug = debug_flags();
   a.wait_limit = wait_limit_cycles();
 
-  const long long total = (long long)a.batch * a.strips_per_batch * a.nchunks;
-  int grid = (int)std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
+  const int grid = plan.grid;
   const bool out32 = p.out_dtype == SSD_F32 && mode == 0;
   const bool seq = in.seq_idx != nullptr;
   SSD_REQUIRE(raw == nullptr || (!seq && mode == 0), SSD_ERR_UNSUPPORTED, "raw dt with seq_idx or in the states-only mode");
@@ -1181,13 +1222,9 @@ int launch_variant(const ssd_fused_state_params_t& p, int mode, cudaStream_t str
       if (nchecked < 16) checked[nchecked++] = reinterpret_cast<const void*>(kern);
     }
   }
-  // A strip longer than a CTA's range would make the CTAs of that strip wait for one another
-  // in turn; then the carry is deferred to a second, small kernel instead.
-  // (Only when the ranges are long: for short ones the chained carry costs next to nothing and
-  // keeps the passed states free of the second rounding that a later correction implies.)
-  const long long per_cta = (total + grid - 1) / grid;
-  // (not with packed sequences: the second pass multiplies decays across a cut and knows nothing of resets)
-  a.defer = (mode == 0 && a.nchunks > per_cta && per_cta >= 16 && in.seq_idx == nullptr) ? 1 : 0;
+  // (see plan_fused: a strip longer than a CTA's range would make the CTAs of that strip wait for one
+  // another in turn; with long ranges the carry is deferred to a second, small kernel instead)
+  a.defer = plan.defer;
   CUtensorMap mdt = mx;                 // a valid map even where the kernel never touches it
   if (raw != nullptr) {
     rc = make_dt_map(&mdt, raw->dt, raw->dt_dtype, in.nheads, in.seqlen, in.batch, raw->dt_stride_l, raw->dt_stride_b,
@@ -1348,9 +1385,12 @@ int launch_fused_fast(const ssd_fused_state_params_t& p, int mode, cudaStream_t 
   SSD_REQUIRE(raw == nullptr || fused_raw_ok(p, *raw), SSD_ERR_UNSUPPORTED,
               "fused tcgen05 kernel cannot compute the cumsum of this dt itself");
   const bool bf16 = p.in.in_dtype == SSD_BF16;
-  if (variant == 2)
-    return bf16 ? launch_variant<__nv_bfloat16, 2>(p, mode, stream, raw) : launch_variant<__half, 2>(p, mode, stream, raw);
-  return bf16 ? launch_variant<__nv_bfloat16, 1>(p, mode, stream, raw) : launch_variant<__half, 1>(p, mode, stream, raw);
+  const FusedPlan plan = plan_fused(p, variant, mode);
+  if (plan.hpc == 2)
+    return bf16 ? launch_variant<__nv_bfloat16, 2>(p, mode, stream, raw, plan)
+                : launch_variant<__half, 2>(p, mode, stream, raw, plan);
+  return bf16 ? launch_variant<__nv_bfloat16, 1>(p, mode, stream, raw, plan)
+              : launch_variant<__half, 1>(p, mode, stream, raw, plan);
 }
 
 // The RAW variant fetches the raw dt with TMA: heads contiguous, base and the position / batch
@@ -1360,13 +1400,12 @@ bool fused_raw_ok(const ssd_fused_state_params_t& p, const ssd_chunk_cumsum_para
   if (variant == 0 || p.in.seq_idx != nullptr) return false;
   // Inside the persistent kernel the cumsum is one warp's work per CTA, which makes a chunk about 6 %
   // slower than when a stand-alone cumsum kernel has run first; what the single launch saves is the
-  // second launch with its ramp and tail, a fixed 5 - 7 us.  Measured on B200 (Mamba2-130M layer shape
-  // 41 vs 48 us, 2.7B shape 120 vs 122 us, 8B-style shape 987 vs 897 us) the two meet at roughly a
+  // second launch with its ramp and tail, a fixed 5 - 7 us.  Measured on B200 (2.7B shape 120 vs 122 us, 8B-style shape 987 vs 897 us) the two meet at roughly a
   // hundred chunks per CTA; beyond that the two launches are used.  The results are the same bits.
   const long long nchunks = (p.in.seqlen + p.in.chunk_size - 1) / p.in.chunk_size;
-  const long long total = (long long)p.in.batch * (p.in.nheads / variant) * nchunks;
-  const long long grid = std::min<long long>(total, std::min(num_sms(), FusedWorkspaceLayout::kMaxCtas));
-  if (grid > 0 && (total + grid - 1) / grid > 96) return false;
+  const FusedPlan plan = plan_fused(p, variant, 0);
+  const long long total = (long long)p.in.batch * (p.in.nheads / plan.hpc) * nchunks;
+  if (plan.grid > 0 && (total + plan.grid - 1) / plan.grid > 96) return false;
   if (raw.dt_stride_h != 1) return false;
   const int es = dtype_size(raw.dt_dtype);
   if (reinterpret_cast<uintptr_t>(raw.dt) % 16 != 0) return false;

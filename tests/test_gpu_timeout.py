@@ -17,7 +17,9 @@ from oracle import ssd_oracle as O
 pytestmark = pytest.mark.gpu
 
 SHORT_LIMIT = 2_000_000          # SM cycles, about one millisecond
-DROP_CARRY_FLAGS = 1             # SSD_DEBUG_DROP_CARRY_FLAGS
+# SSD_DEBUG_DROP_CARRY_FLAGS | SSD_DEBUG_CUT_STRIPS: a problem this small would otherwise run one CTA
+# per head with no carries between CTAs at all
+DROP_CARRY_FLAGS = 1 | 2
 
 
 def _problem(device):
