@@ -1400,8 +1400,9 @@ bool fused_raw_ok(const ssd_fused_state_params_t& p, const ssd_chunk_cumsum_para
   if (variant == 0 || p.in.seq_idx != nullptr) return false;
   // Inside the persistent kernel the cumsum is one warp's work per CTA, which makes a chunk about 6 %
   // slower than when a stand-alone cumsum kernel has run first; what the single launch saves is the
-  // second launch with its ramp and tail, a fixed 5 - 7 us.  Measured on B200 (2.7B shape 120 vs 122 us, 8B-style shape 987 vs 897 us) the two meet at roughly a
-  // hundred chunks per CTA; beyond that the two launches are used.  The results are the same bits.
+  // second launch with its ramp and tail, a fixed 5 - 7 us.  Measured on B200 (2.7B shape 120 vs
+  // 122 us, 8B-style shape 987 vs 897 us) the two meet at roughly a hundred chunks per CTA; beyond
+  // that the two launches are used.  The results are the same bits.
   const long long nchunks = (p.in.seqlen + p.in.chunk_size - 1) / p.in.chunk_size;
   const FusedPlan plan = plan_fused(p, variant, 0);
   const long long total = (long long)p.in.batch * (p.in.nheads / plan.hpc) * nchunks;
