@@ -51,3 +51,17 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(params=["layout_chosen", "layout_ranges_per_sm"])
+def both_layouts(request, cuda_device):
+    """Runs a test twice: with the layout the fused state kernel chooses for the problem (small
+    test problems run one CTA per head over whole strips) and with the test hook
+    SSD_DEBUG_CUT_STRIPS, which forces the layout of large problems (one range of (strip, chunk)
+    items per SM, states carried between CTAs through carry slots and flags) on the same inputs."""
+    from mamba_fused_minimal_b200._ext import C
+    C.debug_set_flags(2 if request.param == "layout_ranges_per_sm" else 0)
+    try:
+        yield request.param
+    finally:
+        C.debug_set_flags(0)

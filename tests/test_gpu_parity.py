@@ -12,7 +12,7 @@ import torch
 from conftest import golden_names, load_golden, rel_err
 from oracle import ssd_oracle as O
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("both_layouts")]
 
 FP32_TOL = 1e-3
 

@@ -13,7 +13,7 @@ import torch
 
 from oracle import ssd_oracle as O
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("both_layouts")]
 
 
 def _fns():

@@ -15,7 +15,7 @@ import torch
 
 from oracle import ssd_oracle as O
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("both_layouts")]
 
 
 def _run_pair(cuda_device, shape, dtype, init, force_general, seeds=(31, 32)):
