@@ -74,6 +74,10 @@ __device__ __forceinline__ float fast_exp(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
   return y;
 }
+// z * sigmoid(z), the gate of kernels/ssd_chunk_scan.py's device code (`out *= z * tl.sigmoid(z)`), with
+// the operations a compiled Triton kernel uses for it: the fast exponential above and the approximate
+// division.  One function for every kernel that gates, so that they agree bit for bit.
+__device__ __forceinline__ float silu_gate(float z) { return z * __fdividef(1.0f, 1.0f + fast_exp(-z)); }
 // 2^y with the same instruction, for callers that have already multiplied by log2 e.
 __device__ __forceinline__ float ex2_approx(float y) {
   float r;

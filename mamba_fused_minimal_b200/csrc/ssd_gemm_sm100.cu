@@ -215,7 +215,8 @@ template <typename T>
 __global__ void __launch_bounds__(kScanThreads, 2)
 chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_constant__ CUtensorMap tmap_S,
                   const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_cb,
-                  const __grid_constant__ CUtensorMap tmap_out, const ScanArgs a) {
+                  const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_outx,
+    const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -416,8 +417,6 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
     if (ok) {
       tc_fence_after();
       const float sm = fast_exp(am);
-      uint8_t* orow = static_cast<uint8_t*>(a.out) +
-                      2 * ((int64_t)b * a.out_s[0] + pos * a.out_s[1] + (int64_t)h * a.out_s[2]) + q * 64;
       uint32_t r1[32], r2[32];
       tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
       tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
@@ -441,10 +440,13 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
           }
         }
       }
-      if (a.z != nullptr && live) {
-        // out_x = the ungated result; out = out_x * z * sigmoid(z)   (ssd_chunk_scan.py device code)
-        uint8_t* oxrow = static_cast<uint8_t*>(a.out_x) +
-                         2 * ((int64_t)b * a.out_s[0] + pos * a.out_s[1] + (int64_t)h * a.out_s[2]) + q * 64;
+      // The result leaves through shared memory as one TMA store per warp: this warp's 32 rows x 32
+      // columns as a 32 x 64-byte box (64-byte swizzle: piece c of row r at piece c ^ ((r / 2) % 4)) in
+      // the C tile's shared memory, which no MMA reads any more.  Rows past the sequence end are clipped
+      // by the tensor map.  With a gate there are two boxes per warp: out_x, the ungated result, and
+      // out = out_x * z * sigmoid(z) (ssd_chunk_scan.py device code).
+      const bool rows_in_range = mt * kScanRows + (warp & 3) * 32 < limit;
+      auto stage_and_store = [&](const CUtensorMap* map, uint32_t off) {
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
           uint4 t;
@@ -452,49 +454,35 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
           t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
           t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
           t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
-          *reinterpret_cast<uint4*>(oxrow + pc * 16) = t;
-          const uint32_t w[4] = {zr[pc].x, zr[pc].y, zr[pc].z, zr[pc].w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float z0, z1;
-            PackPair<T>::unpack(w[i], z0, z1);
-            res[pc * 8 + 2 * i] *= z0 * (1.0f / (1.0f + expf(-z0)));
-            res[pc * 8 + 2 * i + 1] *= z1 * (1.0f / (1.0f + expf(-z1)));
-          }
-        }
-      }
-      if (a.z == nullptr) {
-        // Without a gate the result leaves through shared memory as one TMA store per warp: this warp's
-        // 32 rows x 32 columns as a 32 x 64-byte box (64-byte swizzle: piece c of row r at piece
-        // c ^ ((r / 2) % 4)) in the C tile's shared memory, which no MMA reads any more.
-        uint8_t* stg = smem + warp * (32 * 64);
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          uint4 t;
-          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
-          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
-          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
-          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
-          *reinterpret_cast<uint4*>(stg + lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4)) = t;
+          *reinterpret_cast<uint4*>(smem + off + lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4)) = t;
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && mt * kScanRows + (warp & 3) * 32 < limit) {   // rows past the sequence end are clipped by the map
-          tma_store_4d(&tmap_out, sbase + warp * (32 * 64), q * 32, h, c * L + mt * kScanRows + (warp & 3) * 32, b);
+        if (lane == 0 && rows_in_range) {
+          tma_store_4d(map, sbase + off, q * 32, h, c * L + mt * kScanRows + (warp & 3) * 32, b);
           bulk_commit();
-          bulk_wait_read_all();                                         // the CTA's shared memory goes away with it
         }
-      } else if (live) {
+      };
+      if (a.z != nullptr) {
+        stage_and_store(&tmap_outx, warp * (32 * 64));
+        if (live) {
 #pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          uint4 t;
-          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
-          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
-          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
-          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
-          *reinterpret_cast<uint4*>(orow + pc * 16) = t;
+          for (int pc = 0; pc < 4; ++pc) {
+            const uint32_t w[4] = {zr[pc].x, zr[pc].y, zr[pc].z, zr[pc].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float z0, z1;
+              PackPair<T>::unpack(w[i], z0, z1);
+              res[pc * 8 + 2 * i] *= silu_gate(z0);
+              res[pc * 8 + 2 * i + 1] *= silu_gate(z1);
+            }
+          }
         }
+        stage_and_store(&tmap_out, (8 + warp) * (32 * 64));
+      } else {
+        stage_and_store(&tmap_out, warp * (32 * 64));
       }
+      if (lane == 0) bulk_wait_read_all();                          // the CTA's shared memory goes away with it
     }
   }
   tc_fence_before();
@@ -526,9 +514,9 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
 //     _chunk_scan_fwd.  (Applying the decay below the diagonal as two multiplications,
 //     exp(a_m - a_e) times a per-chunk vector exp(a_e - a_k) dt_k, was measured: 3 % faster, one
 //     element in 10^5 a 16-bit step apart; the exact form is kept.)
-//   * Epilogue without a gate: the x values of the D term come from the staged x tiles (a row's unit
-//     is one of the last two this CTA loaded) and every warp sends its 32 x 32 piece of the output
-//     through shared memory as one TMA store.
+//   * Epilogue: without a gate the x values of the D term come from the staged x tiles (a row's unit
+//     is one of the last two this CTA loaded); every warp sends its 32 x 32 piece of the output (two
+//     pieces with a gate) through shared memory as one TMA store.
 //   * TMA and MMA issue are two threads in two warps: neither waits for the other's barriers.
 constexpr int kFsU = 64;               // positions per unit
 constexpr int kFsBSlots = 2;           // ring of B tiles (released by the cb MMAs)
@@ -540,7 +528,8 @@ template <typename T>
 __global__ void __launch_bounds__(kFsThreads, 2)
 chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_constant__ CUtensorMap tmap_S,
                         const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_B,
-                        const __grid_constant__ CUtensorMap tmap_out, const ScanArgs a) {
+                        const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_outx,
+    const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -764,26 +753,17 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
     const bool live = m < limit;
     const int q = half;
     const int64_t pos = (int64_t)c * L + m;
-    const uint8_t* xrow = static_cast<const uint8_t*>(a.x) +
-                          2 * ((int64_t)b * a.x_s[0] + pos * a.x_s[1] + (int64_t)h * a.x_s[2]) + q * 64;
-    // Without a gate the row's x values come from the staged x tile of its unit (one of the last two
+    // The row's x values for the D term come from the staged x tile of its unit (one of the last two
     // units this CTA loaded, still in the ring: 128-byte rows, 16-byte pieces swizzled by the row index
-    // modulo 8) and the result leaves through shared memory as one TMA store per warp; with a gate the
-    // rows are read and written by their threads, 16 bytes at a time.
-    const bool staged = a.z == nullptr;
+    // modulo 8).
     uint4 xr[4];
     if (a.D != nullptr && live) {                    // requested before the wait, used after it
-      if (staged) {
-        const int ux = m / kFsU;
-        ok = mbar_wait(bar_x_full(ux % kFsXSlots), (ux / kFsXSlots) & 1, wc, kFsWaitXFull);
-        const uint32_t xs = sbase + kOffX + (ux % kFsXSlots) * kXTile + (m & (kFsU - 1)) * 128;
+      const int ux = m / kFsU;
+      ok = mbar_wait(bar_x_full(ux % kFsXSlots), (ux / kFsXSlots) & 1, wc, kFsWaitXFull);
+      const uint32_t xoff = kOffX + (ux % kFsXSlots) * kXTile + (m & (kFsU - 1)) * 128;
 #pragma unroll
-        for (int pc = 0; pc < 4; ++pc)
-          xr[pc] = *reinterpret_cast<const uint4*>(smem + (xs - sbase) + (((q * 4 + pc) ^ (m & 7)) << 4));
-      } else {
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc) xr[pc] = __ldg(reinterpret_cast<const uint4*>(xrow) + pc);
-      }
+      for (int pc = 0; pc < 4; ++pc)
+        xr[pc] = *reinterpret_cast<const uint4*>(smem + xoff + (((q * 4 + pc) ^ (m & 7)) << 4));
     }
     uint4 zr[4];
     if (a.z != nullptr && live) {
@@ -797,8 +777,6 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
     if (ok) {
       tc_fence_after();
       const float sm = fast_exp(am);
-      uint8_t* orow = static_cast<uint8_t*>(a.out) +
-                      2 * ((int64_t)b * a.out_s[0] + pos * a.out_s[1] + (int64_t)h * a.out_s[2]) + q * 64;
       uint32_t r1[32], r2[32];
       tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
       tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
@@ -822,9 +800,13 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
           }
         }
       }
-      if (a.z != nullptr && live) {
-        uint8_t* oxrow = static_cast<uint8_t*>(a.out_x) +
-                         2 * ((int64_t)b * a.out_s[0] + pos * a.out_s[1] + (int64_t)h * a.out_s[2]) + q * 64;
+      // The result leaves through shared memory as one TMA store per warp: this warp's 32 rows x 32
+      // columns as a 32 x 64-byte box (64-byte swizzle: piece c of row r at piece c ^ ((r / 2) % 4)) in
+      // the C tile's shared memory, which no MMA reads any more.  Rows past the sequence end are clipped
+      // by the tensor map.  With a gate there are two boxes per warp: out_x, the ungated result, and
+      // out = out_x * z * sigmoid(z) (ssd_chunk_scan.py device code).
+      const bool rows_in_range = mt * kScanRows + wq * 32 < limit;
+      auto stage_and_store = [&](const CUtensorMap* map, uint32_t off) {
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
           uint4 t;
@@ -832,48 +814,35 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
           t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
           t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
           t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
-          *reinterpret_cast<uint4*>(oxrow + pc * 16) = t;
-          const uint32_t w[4] = {zr[pc].x, zr[pc].y, zr[pc].z, zr[pc].w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float z0, z1;
-            PackPair<T>::unpack(w[i], z0, z1);
-            res[pc * 8 + 2 * i] *= z0 * (1.0f / (1.0f + expf(-z0)));
-            res[pc * 8 + 2 * i + 1] *= z1 * (1.0f / (1.0f + expf(-z1)));
-          }
-        }
-      }
-      if (staged) {
-        // This warp's 32 rows x 32 columns as a 32 x 64-byte box (64-byte swizzle: piece c of row r at
-        // piece c ^ ((r / 2) % 4)) in the C tile's shared memory, which no MMA reads any more.
-        uint8_t* stg = smem + warp * (32 * 64);
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          uint4 t;
-          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
-          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
-          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
-          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
-          *reinterpret_cast<uint4*>(stg + lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4)) = t;
+          *reinterpret_cast<uint4*>(smem + off + lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4)) = t;
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && mt * kScanRows + wq * 32 < limit) {     // rows past the sequence end are clipped by the map
-          tma_store_4d(&tmap_out, sbase + warp * (32 * 64), q * 32, h, c * L + mt * kScanRows + wq * 32, b);
+        if (lane == 0 && rows_in_range) {
+          tma_store_4d(map, sbase + off, q * 32, h, c * L + mt * kScanRows + wq * 32, b);
           bulk_commit();
-          bulk_wait_read_all();                                   // the CTA's shared memory goes away with it
         }
-      } else if (live) {
+      };
+      if (a.z != nullptr) {
+        stage_and_store(&tmap_outx, warp * (32 * 64));
+        if (live) {
 #pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          uint4 t;
-          t.x = PackPair<T>::pack(res[pc * 8], res[pc * 8 + 1]);
-          t.y = PackPair<T>::pack(res[pc * 8 + 2], res[pc * 8 + 3]);
-          t.z = PackPair<T>::pack(res[pc * 8 + 4], res[pc * 8 + 5]);
-          t.w = PackPair<T>::pack(res[pc * 8 + 6], res[pc * 8 + 7]);
-          *reinterpret_cast<uint4*>(orow + pc * 16) = t;
+          for (int pc = 0; pc < 4; ++pc) {
+            const uint32_t w[4] = {zr[pc].x, zr[pc].y, zr[pc].z, zr[pc].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float z0, z1;
+              PackPair<T>::unpack(w[i], z0, z1);
+              res[pc * 8 + 2 * i] *= silu_gate(z0);
+              res[pc * 8 + 2 * i + 1] *= silu_gate(z1);
+            }
+          }
         }
+        stage_and_store(&tmap_out, (8 + warp) * (32 * 64));
+      } else {
+        stage_and_store(&tmap_out, warp * (32 * 64));
       }
+      if (lane == 0) bulk_wait_read_all();                          // the CTA's shared memory goes away with it
     }
   }
   tc_fence_before();
@@ -1018,10 +987,15 @@ int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream
   auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_kernel<__nv_bfloat16> : chunk_scan_kernel<__half>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
-  CUtensorMap mo;
+  CUtensorMap mo, mox;
   rc = make_rows_store_map(&mo, p.out, p.in_dtype, p.nheads, p.seqlen, p.batch, p.out_stride);
   if (rc != SSD_OK) return rc;
-  kern<<<grid, kScanThreads, smem, stream>>>(mC, mS, mx, mcb, mo, a);
+  mox = mo;                             // a valid map even where the kernel never touches it
+  if (p.z != nullptr) {
+    rc = make_rows_store_map(&mox, p.out_x, p.in_dtype, p.nheads, p.seqlen, p.batch, p.out_stride);
+    if (rc != SSD_OK) return rc;
+  }
+  kern<<<grid, kScanThreads, smem, stream>>>(mC, mS, mx, mcb, mo, mox, a);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }
@@ -1086,10 +1060,15 @@ int launch_chunk_scan_fused(const ssd_chunk_scan_fused_params_t& f, cudaStream_t
   auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_fused_kernel<__nv_bfloat16> : chunk_scan_fused_kernel<__half>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
-  CUtensorMap mo;
+  CUtensorMap mo, mox;
   rc = make_rows_store_map(&mo, p.out, p.in_dtype, p.nheads, p.seqlen, p.batch, p.out_stride);
   if (rc != SSD_OK) return rc;
-  kern<<<grid, kFsThreads, smem, stream>>>(mC, mS, mx, mB, mo, a);
+  mox = mo;                             // a valid map even where the kernel never touches it
+  if (p.z != nullptr) {
+    rc = make_rows_store_map(&mox, p.out_x, p.in_dtype, p.nheads, p.seqlen, p.batch, p.out_stride);
+    if (rc != SSD_OK) return rc;
+  }
+  kern<<<grid, kFsThreads, smem, stream>>>(mC, mS, mx, mB, mo, mox, a);
   SSD_CUDA_OK(cudaGetLastError());
   return SSD_OK;
 }

@@ -708,7 +708,7 @@ struct ChunkScanProblem {
     if (p.z) {
       store_f(p.out_x, p.in_dtype, o, acc);
       const float zv = load_f(p.z, p.in_dtype, c.zbase + (int64_t)m * p.z_stride[1] + (int64_t)n * p.z_stride[3]);
-      acc *= zv * (1.0f / (1.0f + expf(-zv)));
+      acc *= silu_gate(zv);
     }
     store_f(p.out, p.in_dtype, o, acc);
   }
