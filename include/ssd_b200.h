@@ -216,9 +216,13 @@ SSD_API int ssd_check_status(void* workspace, ssd_stream_t stream);
  *     This exists to test that path with a short limit; 0 restores normal operation.
  *     SSD_DEBUG_CUT_STRIPS makes the fused kernel always cut its work into one range per SM, also
  *     where a problem has no more (batch, head pair) strips than SMs and would run one CTA per
- *     strip: small test problems then exercise the carry chain between CTAs. */
+ *     strip: small test problems then exercise the carry chain between CTAs.
+ *     SSD_DEBUG_PLAIN_CHUNK_KERNELS sends ssd_bmm_chunk_fwd and ssd_chunk_scan_fwd to the plain kernels
+ *     (and makes ssd_chunk_scan_fused_fwd answer SSD_ERR_UNSUPPORTED) also where the tcgen05 kernels
+ *     would take the problem: the tests compare the two routes on the same inputs with it. */
 #define SSD_DEBUG_DROP_CARRY_FLAGS 1
 #define SSD_DEBUG_CUT_STRIPS 2
+#define SSD_DEBUG_PLAIN_CHUNK_KERNELS 4
 SSD_API void ssd_debug_set_wait_limit_cycles(long long cycles);
 SSD_API void ssd_debug_set_flags(int flags);
 
@@ -339,10 +343,11 @@ SSD_API int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t 
  *    dtype and strides are ignored; B is (b, l, g, n) of scan.in_dtype.
  *
  *    Only the tcgen05 kernel implements this: 16-bit inputs, headdim 64, dstate 128, chunk size
- *    128 or 256, no seq_idx, 16-byte aligned tensors with contiguous innermost dimensions.  For
+ *    128 or 256, 16-byte aligned tensors with contiguous innermost dimensions.  For
  *    anything else the call returns SSD_ERR_UNSUPPORTED and enqueues nothing; the caller then makes
- *    the two separate calls (5) and (6).  Same operations in the same order as the two calls: a
- *    few outputs per million differ from theirs, by one step of the 16-bit output type.
+ *    the two separate calls (5) and (6).  Same operations in the same order as the two calls: the
+ *    output carries the same bits as theirs.  scan.seq_idx (packed sequences) is honoured: products
+ *    between positions of different sequences are dropped on chip as _bmm_chunk_fwd drops them.
  * ---------------------------------------------------------------------------------- */
 typedef struct {
   ssd_chunk_scan_params_t scan;

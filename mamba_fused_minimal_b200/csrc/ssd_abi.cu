@@ -328,7 +328,7 @@ int ssd_bmm_chunk_fwd(const ssd_bmm_chunk_params_t* prm, ssd_stream_t stream) {
   SSD_REQUIRE(valid_dtype(p.in_dtype) && valid_dtype(p.out_dtype), SSD_ERR_BAD_ARGUMENT, "bad dtype");
   SSD_REQUIRE(p.batch > 0 && p.seqlen > 0 && p.ngroups > 0 && p.k > 0 && p.chunk_size > 0, SSD_ERR_BAD_ARGUMENT,
               "sizes must be positive");
-  if (bmm_fast_ok(p)) return launch_bmm_chunk_fast(p, reinterpret_cast<cudaStream_t>(stream));
+  if (bmm_fast_ok(p) && !(debug_flags() & SSD_DEBUG_PLAIN_CHUNK_KERNELS)) return launch_bmm_chunk_fast(p, reinterpret_cast<cudaStream_t>(stream));
   return launch_bmm_chunk_general(p, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -345,7 +345,7 @@ int ssd_chunk_scan_fwd(const ssd_chunk_scan_params_t* prm, ssd_stream_t stream) 
   SSD_REQUIRE(p.batch > 0 && p.seqlen > 0 && p.nheads > 0 && p.headdim > 0 && p.ngroups > 0 && p.dstate > 0 &&
                   p.chunk_size > 0 && p.nheads % p.ngroups == 0,
               SSD_ERR_BAD_ARGUMENT, "bad sizes");
-  if (scan_fast_ok(p)) return launch_chunk_scan_fast(p, reinterpret_cast<cudaStream_t>(stream));
+  if (scan_fast_ok(p) && !(debug_flags() & SSD_DEBUG_PLAIN_CHUNK_KERNELS)) return launch_chunk_scan_fast(p, reinterpret_cast<cudaStream_t>(stream));
   return launch_chunk_scan_general(p, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -361,7 +361,7 @@ int ssd_chunk_scan_fused_fwd(const ssd_chunk_scan_fused_params_t* prm, ssd_strea
   SSD_REQUIRE(p.batch > 0 && p.seqlen > 0 && p.nheads > 0 && p.headdim > 0 && p.ngroups > 0 && p.dstate > 0 &&
                   p.chunk_size > 0 && p.nheads % p.ngroups == 0,
               SSD_ERR_BAD_ARGUMENT, "bad sizes");
-  SSD_REQUIRE(scan_fused_ok(*prm), SSD_ERR_UNSUPPORTED,
+  SSD_REQUIRE(scan_fused_ok(*prm) && !(debug_flags() & SSD_DEBUG_PLAIN_CHUNK_KERNELS), SSD_ERR_UNSUPPORTED,
               "the fused chunk bmm + chunk scan kernel does not take this problem: call ssd_bmm_chunk_fwd and "
               "ssd_chunk_scan_fwd");
   return launch_chunk_scan_fused(*prm, reinterpret_cast<cudaStream_t>(stream));
@@ -372,7 +372,7 @@ int ssd_combined_fwd(const ssd_combined_params_t* prm, ssd_stream_t stream) {
   SSD_REQUIRE(prm != nullptr, SSD_ERR_BAD_ARGUMENT, "params is NULL");
   SSD_REQUIRE(prm->scan.B != nullptr && prm->scan.scan.x != nullptr && prm->scan.scan.C != nullptr, SSD_ERR_BAD_ARGUMENT,
               "B, x and C must not be NULL");
-  SSD_REQUIRE(scan_fused_ok(prm->scan), SSD_ERR_UNSUPPORTED,
+  SSD_REQUIRE(scan_fused_ok(prm->scan) && !(debug_flags() & SSD_DEBUG_PLAIN_CHUNK_KERNELS), SSD_ERR_UNSUPPORTED,
               "the fused chunk bmm + chunk scan kernel does not take this problem: make the separate calls");
   const int rc = ssd_state_path_fwd(&prm->path, stream);
   if (rc != SSD_OK) return rc;

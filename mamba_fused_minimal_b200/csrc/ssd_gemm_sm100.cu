@@ -49,6 +49,7 @@ template <> struct PackPair<__half> {
   }
 };
 
+constexpr int kSeqPad = -2147483647 - 1;   // sequence index of positions past the end: matches nothing
 constexpr int kBmmRows = 128;        // rows i per CTA (the MMA's M)
 constexpr int kBmmThreads = 160;     // 4 epilogue warps + 1 service warp
 
@@ -61,6 +62,9 @@ struct BmmArgs {
   int out_dtype;
   int L, K, ngroups;
   long long wait_limit;              // SM cycles a device-side wait may last
+  const int32_t* seq;                // (b, l) sequence index of each position, or NULL
+  int64_t seq_s[2];
+  int seqlen;
 };
 
 // Status word of the bmm kernel's bounded waits.
@@ -81,11 +85,19 @@ bmm_chunk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t bar_load = sbase + off_ctl, bar_acc = sbase + off_ctl + 8;
   volatile int* ctl = reinterpret_cast<volatile int*>(smem + off_ctl + 16);   // [0] abort, [1] tmem
   WaitCtx wc{ctl, a.status, a.wait_limit};
+  int* seq_sm = reinterpret_cast<int*>(smem + off_ctl + 64);                   // [L], packed sequences only
 
   const int mt = blockIdx.x;
   const int c = blockIdx.y / a.ngroups, g = blockIdx.y % a.ngroups;
   const int b = blockIdx.z;
   const uint32_t ncols = L <= 32 ? 32u : (L <= 64 ? 64u : (L <= 128 ? 128u : 256u));
+  // packed sequences (kernels/ssd_bmm.py:79-83): a product survives only between two positions of the
+  // same sequence; positions past the end of the tensor match nothing
+  if (a.seq != nullptr) {
+    const int limit = min(L, a.seqlen - c * L);
+    for (int k = tid; k < L; k += kBmmThreads)
+      seq_sm[k] = k < limit ? a.seq[(int64_t)b * a.seq_s[0] + (int64_t)(c * L + k) * a.seq_s[1]] : kSeqPad;
+  }
 
   if (tid == 0) {
     mbar_init(bar_load, 1);
@@ -143,7 +155,13 @@ bmm_chunk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int hr = 0; hr < 2; ++hr) {
               const int64_t e = tile + (int64_t)(lh * 16 + gq + hr * 8) * a.out_s[3] + j0 + jj * 8 + 2 * q;
-              const float v0 = __uint_as_float(r[4 * jj + 2 * hr]), v1 = __uint_as_float(r[4 * jj + 2 * hr + 1]);
+              float v0 = __uint_as_float(r[4 * jj + 2 * hr]), v1 = __uint_as_float(r[4 * jj + 2 * hr + 1]);
+              if (a.seq != nullptr) {
+                const int si = seq_sm[mt * kBmmRows + warp * 32 + lh * 16 + gq + hr * 8];
+                const int2 sj = *reinterpret_cast<const int2*>(seq_sm + j0 + jj * 8 + 2 * q);
+                if (si != sj.x || si == kSeqPad) v0 = 0.0f;
+                if (si != sj.y || si == kSeqPad) v1 = 0.0f;
+              }
               if (a.out_dtype == SSD_F32) {
                 *reinterpret_cast<float2*>(static_cast<float*>(a.out) + e) = make_float2(v0, v1);
               } else if (a.out_dtype == SSD_BF16) {
@@ -207,6 +225,8 @@ struct ScanArgs {
   int D_dtype, D_has_hdim;
   int L, seqlen, nheads, ngroups, nchunks;
   long long wait_limit;
+  const int32_t* seq;                  // (b, l) sequence index of each position, or NULL
+  int64_t seq_s[2];
 };
 
 __device__ int g_scan_status[4];
@@ -416,7 +436,15 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_const
     if (ok) ok = mbar_wait(bar_acc, 0, wc, kScanWaitAcc, 64);
     if (ok) {
       tc_fence_after();
-      const float sm = fast_exp(am);
+      float sm = fast_exp(am);
+      // packed sequences (kernels/ssd_chunk_scan.py:104-108): the state carried into the chunk belongs to
+      // the sequence of the previous chunk's last position (sequence 0 before the first chunk)
+      if (a.seq != nullptr) {
+        const int64_t sb = (int64_t)b * a.seq_s[0];
+        const int prev = c > 0 ? a.seq[sb + (int64_t)(c * L - 1) * a.seq_s[1]] : 0;
+        const int mine = live ? a.seq[sb + pos * a.seq_s[1]] : -1;
+        if (mine != prev) sm = 0.0f;
+      }
       uint32_t r1[32], r2[32];
       tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
       tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
@@ -524,7 +552,7 @@ constexpr int kFsXSlots = 3;           // ring of x tiles (released by the acc2 
 constexpr int kFsThreads = (kScanRowWarps + 2) * 32;
 enum FusedScanWait { kFsWaitCbFull = 311, kFsWaitCbFree, kFsWaitBFull, kFsWaitBFree, kFsWaitXFull, kFsWaitXFree };
 
-template <typename T>
+template <typename T, bool SEQ>
 __global__ void __launch_bounds__(kFsThreads, 2)
 chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid_constant__ CUtensorMap tmap_S,
                         const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_B,
@@ -540,9 +568,10 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
   constexpr uint32_t kBTile = 2 * kBBox, kXTile = kFsU * 128;                 // 16 KiB, 8 KiB
   constexpr uint32_t kOffS = 2 * kCBox, kOffB = kOffS + 2 * kSBox, kOffX = kOffB + kFsBSlots * kBTile;
   constexpr uint32_t kOffVec = kOffX + kFsXSlots * kXTile;
-  constexpr uint32_t kOffCtl = kOffVec + 2 * 256 * 4;
+  constexpr uint32_t kOffCtl = kOffVec + 3 * 256 * 4;
   float* dA_s = reinterpret_cast<float*>(smem + kOffVec);
   float* dt_s = dA_s + 256;
+  int* seq_sm = reinterpret_cast<int*>(dt_s + 256);         // packed sequences only
   const uint32_t bars = sbase + kOffCtl;
   const uint32_t bar_cs = bars, bar_acc = bars + 8, bar_cb_full = bars + 16, bar_cb_free = bars + 24;
   auto bar_b_full = [&](int i) { return bars + 32 + 8u * i; };
@@ -602,6 +631,8 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
     for (int k = tid; k < L; k += kScanRowWarps * 32) {
       dA_s[k] = dAr[k];
       dt_s[k] = dtr[k];
+      if constexpr (SEQ)
+        seq_sm[k] = k < limit ? a.seq[(int64_t)b * a.seq_s[0] + (int64_t)(c * L + k) * a.seq_s[1]] : kSeqPad;
     }
   }
   tc_fence_before();
@@ -686,6 +717,11 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
     const float am = dA_s[min(m, L - 1)];
     const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
     const int udiag = (mt * kScanRows + wq * 32) / kFsU;   // the unit that holds this warp's rows
+    // packed sequences (kernels/ssd_bmm.py:79-83): cb[m, k] counts only between positions of one sequence
+    int sq_m = kSeqPad + 1;
+    if constexpr (SEQ) {
+      if (m < limit) sq_m = seq_sm[m];
+    }
     bool ok = true;
     for (int u = 0; u < nu && ok; ++u) {
       const int k0 = u * kFsU + half * 32;
@@ -734,6 +770,16 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
           for (int i = 0; i < 32; ++i)
             if (k0 + i > m) v[i] = 0.0f;
         }
+        if constexpr (SEQ) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const int4 sk = *reinterpret_cast<const int4*>(seq_sm + k0 + i);
+            if (sk.x != sq_m) v[i] = 0.0f;
+            if (sk.y != sq_m) v[i + 1] = 0.0f;
+            if (sk.z != sq_m) v[i + 2] = 0.0f;
+            if (sk.w != sq_m) v[i + 3] = 0.0f;
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) o[i] = PackPair<T>::pack(v[2 * i], v[2 * i + 1]);
       }
@@ -776,7 +822,15 @@ chunk_scan_fused_kernel(const __grid_constant__ CUtensorMap tmap_C, const __grid
     if (ok) ok = mbar_wait(bar_acc, 0, wc, kScanWaitAcc, 64);
     if (ok) {
       tc_fence_after();
-      const float sm = fast_exp(am);
+      float sm = fast_exp(am);
+      // packed sequences (kernels/ssd_chunk_scan.py:104-108): the state carried into the chunk belongs to
+      // the sequence of the previous chunk's last position (sequence 0 before the first chunk)
+      if (a.seq != nullptr) {
+        const int64_t sb = (int64_t)b * a.seq_s[0];
+        const int prev = c > 0 ? a.seq[sb + (int64_t)(c * L - 1) * a.seq_s[1]] : 0;
+        const int mine = live ? a.seq[sb + pos * a.seq_s[1]] : -1;
+        if (mine != prev) sm = 0.0f;
+      }
       uint32_t r1[32], r2[32];
       tmem_ld_32x32(tmem_base + lane_sel + kAcc1 + q * 32, r1);
       tmem_ld_32x32(tmem_base + lane_sel + kAcc2 + q * 32, r2);
@@ -871,7 +925,6 @@ int gemm_wait_status(int* code) {
 // 1 if the tcgen05 kernel takes this problem (otherwise the plain kernel does).
 int bmm_fast_ok(const ssd_bmm_chunk_params_t& p) {
   if (p.in_dtype != SSD_BF16 && p.in_dtype != SSD_F16) return 0;
-  if (p.seq_idx != nullptr) return 0;
   if (p.chunk_size != 128 && p.chunk_size != 256) return 0;
   if (p.k != 64 && p.k != 128) return 0;
   if (p.a_stride[3] != 1 || p.b_stride[3] != 1 || p.out_stride[4] != 1) return 0;
@@ -903,8 +956,12 @@ int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream) 
   a.K = p.k;
   a.ngroups = p.ngroups;
   a.wait_limit = wait_limit_cycles();
+  a.seq = p.seq_idx;
+  a.seq_s[0] = p.seq_idx_stride[0];
+  a.seq_s[1] = p.seq_idx_stride[1];
+  a.seqlen = p.seqlen;
   const int kboxes = p.k / 64;
-  const int smem = kboxes * (kBmmRows * 128 + L * 128) + 64 + 1024;
+  const int smem = kboxes * (kBmmRows * 128 + L * 128) + 64 + L * 4 + 1024;
   auto kern = p.in_dtype == SSD_BF16 ? bmm_chunk_kernel<__nv_bfloat16> : bmm_chunk_kernel<__half>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kBmmRows, nchunks * p.ngroups, p.batch);
@@ -918,7 +975,6 @@ int launch_bmm_chunk_fast(const ssd_bmm_chunk_params_t& p, cudaStream_t stream) 
 int scan_fast_ok(const ssd_chunk_scan_params_t& p) {
   if (p.in_dtype != SSD_BF16 && p.in_dtype != SSD_F16) return 0;
   if (p.states_dtype != p.in_dtype || p.cb_dtype != SSD_F32) return 0;
-  if (p.seq_idx != nullptr) return 0;
   if (p.z != nullptr) {
     if (p.out_x == nullptr || p.z_stride[3] != 1 || (reinterpret_cast<uintptr_t>(p.z) & 15) ||
         (reinterpret_cast<uintptr_t>(p.out_x) & 15))
@@ -982,6 +1038,9 @@ int launch_chunk_scan_fast(const ssd_chunk_scan_params_t& p, cudaStream_t stream
   a.ngroups = p.ngroups;
   a.nchunks = nchunks;
   a.wait_limit = wait_limit_cycles();
+  a.seq = p.seq_idx;
+  a.seq_s[0] = p.seq_idx_stride[0];
+  a.seq_s[1] = p.seq_idx_stride[1];
   const int smem = 2 * kScanRows * 128 + 2 * kScanP * 128 + kScanSlots * (kScanRows * kScanU * 4 + kScanU * 128) +
                    2 * 256 * 4 + 128 + 1024;
   auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_kernel<__nv_bfloat16> : chunk_scan_kernel<__half>;
@@ -1055,9 +1114,14 @@ int launch_chunk_scan_fused(const ssd_chunk_scan_fused_params_t& f, cudaStream_t
   a.ngroups = p.ngroups;
   a.nchunks = nchunks;
   a.wait_limit = wait_limit_cycles();
+  a.seq = p.seq_idx;
+  a.seq_s[0] = p.seq_idx_stride[0];
+  a.seq_s[1] = p.seq_idx_stride[1];
   const int smem = 2 * kScanRows * 128 + 2 * kScanP * 128 + kFsBSlots * 2 * kFsU * 128 + kFsXSlots * kFsU * 128 +
-                   2 * 256 * 4 + 256 + 1024;
-  auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_fused_kernel<__nv_bfloat16> : chunk_scan_fused_kernel<__half>;
+                   3 * 256 * 4 + 256 + 1024;
+  auto kern = p.in_dtype == SSD_BF16 ? chunk_scan_fused_kernel<__nv_bfloat16, false> : chunk_scan_fused_kernel<__half, false>;
+  if (p.seq_idx != nullptr)
+    kern = p.in_dtype == SSD_BF16 ? chunk_scan_fused_kernel<__nv_bfloat16, true> : chunk_scan_fused_kernel<__half, true>;
   SSD_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(L / kScanRows, p.nheads, p.batch * nchunks);
   CUtensorMap mo, mox;

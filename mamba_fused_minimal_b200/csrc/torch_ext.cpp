@@ -692,8 +692,7 @@ std::tuple<Tensor, OptTensor> chunk_scan_combined_fwd(const Tensor& C, const Ten
   TORCH_CHECK(x.dim() == 4 && B.dim() == 4 && C.dim() == 4 && dt.dim() == 4 && states.dim() == 5 && B.sizes() == C.sizes(),
               "x (b, l, h, p), B and C (b, l, g, n), dt (b, h, c, L), states (b, c, h, p, n)");
   const int64_t chunk_size = dt.size(3);
-  bool try_fused = !seq_idx.has_value();
-  if (try_fused) {
+  {
     c10::cuda::CUDAGuard guard(x.device());
     Tensor out = alloc_out({x.size(0), x.size(1), x.size(2), x.size(3)}, x.options());
     OptTensor out_x;
@@ -740,6 +739,15 @@ std::tuple<Tensor, OptTensor> chunk_scan_combined_fwd(const Tensor& C, const Ten
       copy_strides(p.z_stride, zh, {0, 1, 2, 3});
       out_x = alloc_out(out.sizes(), out.options());
       p.out_x = out_x->data_ptr();
+    }
+    Tensor sih;
+    if (seq_idx.has_value()) {
+      check_cuda(*seq_idx, x, "seq_idx");
+      TORCH_CHECK(seq_idx->dim() == 2, "seq_idx must be (batch, seqlen)");
+      sih = as_int32(*seq_idx);
+      p.seq_idx = sih.data_ptr<int32_t>();
+      p.seq_idx_stride[0] = sih.stride(0);
+      p.seq_idx_stride[1] = sih.stride(1);
     }
     const int rc = ssd_chunk_scan_fused_fwd(&f, current_stream(x));
     if (rc == SSD_OK) return {out, out_x};
