@@ -560,6 +560,17 @@ def run_forward(args, rank, world, local):
     torch.cuda.synchronize()
     kernels["bmm_chunk_ms"] = statistics.median(e[0].elapsed_time(e[1]) for e in evs)
     kernels["chunk_scan_ms"] = statistics.median(e[1].elapsed_time(e[2]) for e in evs)
+    # the same two with the z gate (out_x and out = out_x * z * sigmoid(z))
+    z = torch.randn_like(x)
+    for e in evs:
+        e[0].record()
+        bmm_scan(C, B, x, dto, dA, passed, D=D, z=z)
+        e[1].record()
+        scan(cb, x, dto, dA, C, passed, D=D, z=z)
+        e[2].record()
+    torch.cuda.synchronize()
+    kernels["bmm_chunk_scan_one_kernel_gated_ms"] = statistics.median(e[0].elapsed_time(e[1]) for e in evs)
+    kernels["chunk_scan_gated_ms"] = statistics.median(e[1].elapsed_time(e[2]) for e in evs)
     from mamba_fused_minimal_b200._ext import C as _C
     _C.check_status(x)
     if rank == 0:
