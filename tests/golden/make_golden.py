@@ -65,6 +65,8 @@ GPU_CASES = {
     "bf16_small": (2, 384, 4, 64, 2, 128, 128, dict(softplus=True, bias=True, D="h", init=True)),
     "bf16_ragged": (1, 300, 3, 64, 1, 64, 64, dict(softplus=True, bias=True, D="hp", z=True)),
     "fp16_small": (1, 256, 2, 32, 1, 32, 64, dict(softplus=True, bias=True, D="h")),
+    # packed sequences + gate + ragged last chunk at a shape every tcgen05 kernel takes
+    "bf16_packed": (1, 400, 2, 64, 1, 128, 128, dict(softplus=True, bias=True, D="hp", z=True, seq_idx=True)),
 }
 
 
@@ -129,6 +131,7 @@ def main():
     ap.add_argument("--reference", required=True)
     ap.add_argument("--mode", choices=["interp", "gpu"], required=True)
     ap.add_argument("--out", default=HERE)
+    ap.add_argument("--only", default=None, help="write this one case only")
     args = ap.parse_args()
     if args.mode == "interp":
         os.environ["TRITON_INTERPRET"] = "1"
@@ -149,6 +152,8 @@ def main():
                 if isinstance(getattr(obj, "configs", None), list):
                     obj.configs = obj.configs[-1:]
         for name, case in CASES.items():
+            if args.only not in (None, name):
+                continue
             opt = case[-1]
             d = build_inputs(case, torch.float32, "cpu")
             res = run_reference(mods, d, case[6], opt)
@@ -173,6 +178,8 @@ def main():
                  softplus=torch.tensor(int(opt.get("softplus", False))), **d, **res)
     else:
         for name, case in GPU_CASES.items():
+            if args.only not in (None, name):
+                continue
             opt = case[-1]
             dtype = torch.float16 if name.startswith("fp16") else torch.bfloat16
             d = build_inputs(case, dtype, "cuda")
